@@ -89,13 +89,14 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim
     v_cache[page, :, off] = v
 
 
-def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scale, window, out) -> None:
+def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scale, window, out, sinks=None) -> None:
     """Per request: gather its keys and values from the pages in position order, then plain
     causal (windowed) attention for its new tokens (upstream src/tinyserve/attention.py:62-111)."""
     t, hq, d = q.shape
     hkv = k_cache.shape[1]
     group = hq // hkv
-    res = torch.zeros(t, hq, d, dtype=torch.float32, device=q.device)
+    dv = v_cache.shape[3]
+    res = torch.zeros(t, hq, dv, dtype=torch.float32, device=q.device)
     cu = ctx.cu_query_lens.tolist()
     lens = ctx.context_lens_dev.tolist()
     for b in range(ctx.num_seqs):
@@ -114,8 +115,14 @@ def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scal
             hidden = hidden | (pos[None, :] <= qpos[:, None] - window)
         s = torch.einsum("ihd,jhd->hij", q[r0: r0 + n].float(), k) * scale
         s = s.masked_fill(hidden, float("-inf"))
-        res[r0: r0 + n] = torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), v)
-    out.copy_(res.view(t, hq * d).to(out.dtype))
+        if sinks is not None:
+            # one more column that holds the head's sink logit and carries no value
+            s = torch.cat([s, sinks.float()[:, None, None].expand(hq, n, 1)], dim=-1)
+            p = torch.softmax(s, -1)[..., :-1]
+        else:
+            p = torch.softmax(s, -1)
+        res[r0: r0 + n] = torch.einsum("hij,jhd->ihd", p, v)
+    out.copy_(res.view(t, hq * dv).to(out.dtype))
 
 
 def gemm(x, w, out) -> None:
@@ -130,6 +137,142 @@ def gemm_swiglu(x, w_gate_up, out, arena=None) -> None:
     gu = torch.empty(x.shape[0], 2 * inter, dtype=x.dtype, device=x.device)
     gemm(x, w_gate_up, gu)
     silu_mul(gu, out)
+
+
+# ------------------------------------------------------------- hyper-connections
+def _hc_rebuilt(lanes, fresh, delta, mix_prev, out_prev):
+    if fresh is not None:
+        return fresh[None].expand(lanes.shape[0], -1, -1).clone()
+    if delta is None:
+        return lanes.clone()
+    return torch.einsum("st,sih->tih", mix_prev, lanes) + out_prev[:, None, None] * delta.float()[None]
+
+
+def hc_mix_norm(lanes, fresh, delta, mix_prev, out_prev, in_next, norm_weight, eps, out) -> None:
+    new = _hc_rebuilt(lanes, fresh, delta, mix_prev, out_prev)
+    lanes.copy_(new)
+    u = torch.einsum("s,sih->ih", in_next, new)
+    out.copy_((u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps) * norm_weight.float()).to(out.dtype))
+
+
+def hc_collapse(lanes, fresh, delta, mix_prev, out_prev, rows, out) -> None:
+    total = _hc_rebuilt(lanes, fresh, delta, mix_prev, out_prev).sum(0)
+    out.copy_(total if rows is None else total[rows.long()])
+
+
+# ---------------------------------------------------------------------------- gates
+def act_mul(gate_up, out, activation) -> None:
+    inter = out.shape[1]
+    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    if activation == "silu":
+        a = g * torch.sigmoid(g)
+    else:
+        a = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    out.copy_((a * u).to(out.dtype))
+
+
+def softcap(logits, cap) -> None:
+    logits.copy_(cap * torch.tanh(logits / cap))
+
+
+def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out) -> None:
+    t, heads, w = x.shape
+    y = x.float()
+    if normalise:
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * (weight.float().view(heads, w) if weight_per_head else weight.float().view(1, w))
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float().reshape(t, heads, w))
+    out.copy_(y.reshape(out.shape).to(out.dtype))
+
+
+# ----------------------------------------------------------------- recurrent mixers
+def mlstm_state_size(heads, d, dv) -> int:
+    return heads * (d * dv + -(-dv // 32) * (d + 1))
+
+
+def mlstm_scan(qkv, q_off, k_off, v_off, gates, gate_bias, cap, q_scale, state, ctx, heads, d, dv, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    nblk = -(-dv // 32)
+    per_head = d * dv + nblk * (d + 1)
+    x = qkv.float()
+    for b in range(ctx.num_seqs):
+        st = state[slots[b]].view(heads, per_head)
+        for h in range(heads):
+            S = st[h, : d * dv].view(d, dv).clone()
+            n = st[h, d * dv: d * dv + d].clone()
+            m = st[h, d * dv + d].clone()
+            for t in range(cu[b], cu[b + 1]):
+                q = x[t, q_off + h * d: q_off + (h + 1) * d] * q_scale
+                k = x[t, k_off + h * d: k_off + (h + 1) * d]
+                v = x[t, v_off + h * dv: v_off + (h + 1) * dv]
+                li = cap * torch.tanh((gates[t, h] + gate_bias[h]) / cap)
+                lf = torch.nn.functional.logsigmoid(cap * torch.tanh((gates[t, heads + h] + gate_bias[heads + h]) / cap))
+                m_new = torch.maximum(lf + m, li)
+                keep, take = torch.exp(lf + m - m_new), torch.exp(li - m_new)
+                S = keep * S + take * torch.outer(k, v)
+                n = keep * n + take * k
+                m = m_new
+                out[t, h] = (S.t() @ q) / (torch.maximum((n @ q).abs(), torch.exp(-m)) + 1e-6)
+            st[h, : d * dv] = S.reshape(-1)
+            for blk in range(nblk):
+                base = d * dv + blk * (d + 1)
+                st[h, base: base + d] = n
+                st[h, base + d] = m
+
+
+def delta_scan(qkv, q_off, k_off, v_off, a, dt_bias, a_log, beta_pre, q_scale, state, ctx, heads, kv_heads, d, dv, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    rep = heads // kv_heads
+    for b in range(ctx.num_seqs):
+        st = state[slots[b]].view(heads, d, dv)
+        for h in range(heads):
+            g = h // rep
+            S = st[h].clone()
+            rate = torch.exp(a_log[h])
+            for t in range(cu[b], cu[b + 1]):
+                q = qkv[t, q_off + g * d: q_off + (g + 1) * d]
+                k = qkv[t, k_off + g * d: k_off + (g + 1) * d]
+                v = qkv[t, v_off + h * dv: v_off + (h + 1) * dv]
+                q = q / torch.sqrt(q.pow(2).sum() + 1e-6) * q_scale
+                k = k / torch.sqrt(k.pow(2).sum() + 1e-6)
+                decay = torch.exp(-rate * torch.nn.functional.softplus(a[t, h * d: (h + 1) * d] + dt_bias[h * d: (h + 1) * d]))
+                S = decay[:, None] * S
+                u = torch.sigmoid(beta_pre[t, h]) * (v - S.t() @ k)
+                S = S + torch.outer(k, u)
+                out[t, h] = S.t() @ q
+            st[h] = S
+
+
+def causal_conv_silu(x, taps, state, ctx, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    c, k = taps.shape
+    for b in range(ctx.num_seqs):
+        lo, hi = cu[b], cu[b + 1]
+        seq = torch.cat([state[slots[b]].view(k - 1, c), x[lo:hi].float()])
+        y = sum(seq[j: j + hi - lo] * taps[:, j].float()[None, :] for j in range(k))
+        out[lo:hi] = y * torch.sigmoid(y)
+        if k > 1:
+            state[slots[b]] = seq[-(k - 1):].reshape(-1)
+
+
+def qkv_prepare(q_in, k_in, v_in, q_weight, k_weight, eps, cos, sin, rotary_dim, slots, k_cache, v_cache, page_size,
+                heads, kv_heads, d, dv, q_out) -> None:
+    t = q_out.shape[0]
+
+    def prep(x, w, n):
+        y = x.float().reshape(t, n, d)
+        if w is not None:
+            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        return _rotate(y, cos, sin, rotary_dim, False)
+
+    q_out.copy_(prep(q_in, q_weight, heads).to(q_out.dtype))
+    if k_in is None:
+        return
+    page, off = slots.long() // page_size, slots.long() % page_size
+    k_cache[page, :, off] = prep(k_in, k_weight, kv_heads).to(k_cache.dtype)
+    v_cache[page, :, off] = v_in.reshape(t, kv_heads, dv)
 
 
 # ---------------------------------------------------------------------- sampling
@@ -198,7 +341,8 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, st
 
 
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
-          "gemm", "gemm_simt", "gemm_swiglu", "sample"]
+          "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
+          "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare"]
 
 
 @contextmanager

@@ -1,6 +1,7 @@
 """Architectures this framework serves. Importing the package registers them."""
 
-from . import qwen3  # noqa: F401  (registers Qwen3ForCausalLM)
+from . import fegilix, qwen3  # noqa: F401  (registers Fegilix and Qwen3ForCausalLM)
+from .fegilix import FegilixConfig
 from .qwen3 import Qwen3Config
 
-__all__ = ["Qwen3Config"]
+__all__ = ["FegilixConfig", "Qwen3Config"]

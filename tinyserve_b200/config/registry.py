@@ -38,6 +38,8 @@ def config_class_for(name: str) -> type[ModelConfig]:
 
 def config_from_dict(d: Mapping[str, Any]) -> ModelConfig:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]          # some configurations name their one architecture as a string
     if not isinstance(archs, (list, tuple)) or not archs:
         raise UnsupportedConfigError(
             f"config.json has no 'architectures' list; known: {known_architectures()}"

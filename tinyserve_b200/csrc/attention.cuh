@@ -23,10 +23,37 @@ struct AttnArgs {
   int num_splits;
   float* part_acc;         // [num_seqs, num_heads, num_splits, head_dim]
   float* part_ml;          // [num_seqs, num_heads, num_splits, 2]  (max, sum)
+  // Optional extras (kernels that do not know them leave them at their defaults).
+  const float* sinks = nullptr;  // [num_heads] a logit per head that joins the softmax's denominator without a value
+  int v_head_dim = 0;            // size of a value head when it differs from head_dim (0: the same)
 };
+
+// The finished row: num / den, where the denominator also takes 2^(sink - max) when the head has
+// a sink logit (given in natural units; the running maximum `mx` is in base-2 units).
+__device__ __forceinline__ float finish_row(float num, float den, float mx, const float* sinks, int head) {
+  if (!sinks) return num / den;
+  const float sl = sinks[head] * 1.4426950408889634f;
+  const float top = fmaxf(mx, sl);
+  const float c = (mx == -INFINITY) ? 0.f : exp2f(mx - top);
+  return num * c / (den * c + exp2f(sl - top));
+}
 
 __device__ __forceinline__ size_t kv_offset(int page, int kvh, int off, const AttnArgs& a) {
   return (((size_t)page * a.num_kv_heads + kvh) * a.page_size + off) * a.head_dim;
+}
+
+// Row index (in units of one head's elements) of position `kpos` of a request for kv head `kvh`.
+__device__ __forceinline__ size_t kv_row_of(const int* table, int kpos, int kvh, const AttnArgs& a) {
+  int page, off;
+  if (a.page_shift >= 0) {
+    page = table[kpos >> a.page_shift];
+    off = kpos & (a.page_size - 1);
+  } else {
+    const int idx = kpos / a.page_size;
+    page = table[idx];
+    off = kpos - idx * a.page_size;
+  }
+  return ((size_t)page * a.num_kv_heads + kvh) * a.page_size + off;
 }
 
 // Element offset of position `kpos` of a request (block table `table`) for kv head `kvh`.
@@ -88,7 +115,7 @@ __device__ __forceinline__ void merge_splits(const AttnArgs& a, int si, int qrow
       num += __ldcg(acc + (size_t)sp * D) * c;
       den += mlr[sp * 2 + 1] * c;
     }
-    ((T*)a.out)[((size_t)qrow * a.num_heads + head0 + r) * D + d] = from_float<T>(num / den);
+    ((T*)a.out)[((size_t)qrow * a.num_heads + head0 + r) * D + d] = from_float<T>(finish_row(num, den, mm, a.sinks, head0 + r));
   }
 }
 

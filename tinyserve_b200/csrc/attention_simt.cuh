@@ -31,11 +31,12 @@ template <typename T, int DJMAX>
 __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   extern __shared__ float smem[];
   const int D = a.head_dim;
+  const int DV = a.v_head_dim ? a.v_head_dim : D;   // values may have a head size of their own
   const int DS = D + 1;                         // padded row stride
   float* Qs = smem;                             // [TQ][DS]  pre-scaled queries
   float* Ks = Qs + PF_TQ * DS;                  // [TK][DS]
-  float* Vs = Ks + PF_TK * DS;                  // [TK][D]
-  float* Ss = Vs + PF_TK * D;                   // [TQ][TK + 1]
+  float* Vs = Ks + PF_TK * DS;                  // [TK][DV]
+  float* Ss = Vs + PF_TK * DV;                  // [TQ][TK + 1]
   float* row_m = Ss + PF_TQ * (PF_TK + 1);      // [TQ]
   float* row_l = row_m + PF_TQ;                 // [TQ]
   float* row_c = row_l + PF_TQ;                 // [TQ] correction factor of this tile
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < DJMAX; ++j) acc[i][j] = 0.f;
-  const int dj = D >> 4;
+  const int dj = DV >> 4;
 
   const int qpos_first = first_pos + q0;
   const int qpos_last = first_pos + q0 + nq - 1;
@@ -80,31 +81,29 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   if (a.window > 0) k_lo = max(0, qpos_first - a.window + 1);
   const int k_begin = (k_lo / PF_TK) * PF_TK;
   constexpr int VEC = Vec<T>::N;
-  const int chunks = D / VEC;
+  const int chunks = D / VEC, vchunks = DV / VEC;
 
   for (int k0 = k_begin; k0 <= qpos_last; k0 += PF_TK) {
     __syncthreads();   // previous tile fully consumed (and Qs/row state initialised)
     // ---- stage keys and values k0 .. k0+TK-1 (zeros outside the request's visible range)
-    for (int idx = tid; idx < PF_TK * chunks; idx += PF_THREADS) {
-      const int kk = idx / chunks, c = idx - kk * chunks;
+    for (int idx = tid; idx < PF_TK * (chunks + vchunks); idx += PF_THREADS) {
+      const int kk = idx / (chunks + vchunks), c = idx - kk * (chunks + vchunks);
+      const bool is_key = c < chunks;
+      const int cc = is_key ? c : c - chunks;
       const int kpos = k0 + kk;
-      float kf[VEC], vf[VEC];
+      float f[VEC];
       if (kpos >= k_lo && kpos <= qpos_last) {
-        const size_t off = kv_offset_of(table, kpos, kvh, a) + (size_t)c * VEC;
-        Vec<T> kv, vv;
-        kv.load(kc + off);
-        vv.load(vc + off);
-        kv.unpack(kf);
-        vv.unpack(vf);
+        const size_t row = kv_row_of(table, kpos, kvh, a);
+        Vec<T> raw;
+        raw.load(is_key ? kc + row * D + (size_t)cc * VEC : vc + row * DV + (size_t)cc * VEC);
+        raw.unpack(f);
       } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
+        for (int e = 0; e < VEC; ++e) f[e] = 0.f;
       }
+      float* dst = is_key ? Ks + kk * DS + cc * VEC : Vs + kk * DV + cc * VEC;
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        Ks[kk * DS + c * VEC + e] = kf[e];
-        Vs[kk * D + c * VEC + e] = vf[e];
-      }
+      for (int e = 0; e < VEC; ++e) dst[e] = f[e];
     }
     __syncthreads();
     // ---- scores: thread (ty, tx) owns rows ty*4..+3, keys tx*2..+1
@@ -178,7 +177,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
 #pragma unroll
       for (int j = 0; j < DJMAX; ++j) {
         if (j < dj) {
-          const float vv = Vs[kk * D + tx + 16 * j];
+          const float vv = Vs[kk * DV + tx + 16 * j];
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i][j] = fmaf(p[i], vv, acc[i][j]);
         }
@@ -191,11 +190,11 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   for (int i = 0; i < 4; ++i) {
     const int r = ty * 4 + i;
     if (r < nq) {
-      const float inv = 1.f / row_l[r];
 #pragma unroll
       for (int j = 0; j < DJMAX; ++j)
         if (j < dj)
-          out[((size_t)(row0 + q0 + r) * a.num_heads + head) * D + tx + 16 * j] = from_float<T>(acc[i][j] * inv);
+          out[((size_t)(row0 + q0 + r) * a.num_heads + head) * DV + tx + 16 * j] =
+              from_float<T>(finish_row(acc[i][j], row_l[r], row_m[r], a.sinks, head));
     }
   }
 }
@@ -402,7 +401,7 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
     }
     const int head = kvh * G + g0 + g;
     if (a.num_splits == 1) {
-      ((T*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = from_float<T>(num / den);
+      ((T*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = from_float<T>(finish_row(num, den, mm, a.sinks, head));
     } else {
       const size_t pidx = ((size_t)si * a.num_heads + head) * a.num_splits + split;
       a.part_acc[pidx * D + d] = num;
@@ -419,8 +418,8 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
 
 template <typename T, int DJMAX>
 static int launch_prefill_dj(const AttnArgs& a, int max_query_len, cudaStream_t stream) {
-  const int D = a.head_dim;
-  const size_t smem = sizeof(float) * ((size_t)PF_TQ * (D + 1) + (size_t)PF_TK * (D + 1) + (size_t)PF_TK * D +
+  const int D = a.head_dim, DV = a.v_head_dim ? a.v_head_dim : D;
+  const size_t smem = sizeof(float) * ((size_t)PF_TQ * (D + 1) + (size_t)PF_TK * (D + 1) + (size_t)PF_TK * DV +
                                        (size_t)PF_TQ * (PF_TK + 1) + 3 * PF_TQ);
   auto kern = prefill_attn_kernel<T, DJMAX>;
   if (smem > 48 * 1024) {
@@ -433,7 +432,7 @@ static int launch_prefill_dj(const AttnArgs& a, int max_query_len, cudaStream_t 
 
 template <typename T>
 static int launch_prefill(const AttnArgs& a, int max_query_len, cudaStream_t stream) {
-  const int dj = a.head_dim / 16;
+  const int dj = (a.v_head_dim ? a.v_head_dim : a.head_dim) / 16;
   if (dj <= 2) return launch_prefill_dj<T, 2>(a, max_query_len, stream);
   if (dj <= 4) return launch_prefill_dj<T, 4>(a, max_query_len, stream);
   if (dj <= 8) return launch_prefill_dj<T, 8>(a, max_query_len, stream);

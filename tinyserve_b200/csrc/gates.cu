@@ -1,0 +1,125 @@
+// Gating and squashing kernels: a gated feed-forward's activation with a choice of activation,
+// the per-head RMSNorm and sigmoid output gate that follows a mixer's read-out, and the tanh
+// soft cap of the logits. All arithmetic is 32-bit with one rounding to the output type.
+#define TS_PDL_CLASS PDL_ELEMENTWISE
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int ACT_SILU = 0, ACT_GELU_TANH = 1;
+
+__device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z)); }
+
+template <int ACT>
+__device__ __forceinline__ float activate(float z) {
+  if (ACT == ACT_SILU) return z / (1.f + expf(-z));
+  // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return 0.5f * z * (1.f + tanhf(inner));
+}
+
+// out[t, j] = act(gate_up[t, j]) * gate_up[t, I + j]
+template <typename T, int ACT>
+__global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int j = (int)(idx - t * inter);
+    const T* row = gate_up + t * 2 * (size_t)inter;
+    out[idx] = from_float<T>(activate<ACT>(to_float(row[j])) * to_float(row[inter + j]));
+  }
+}
+
+// logits <- cap * tanh(logits / cap), in place
+__global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    x[idx] = cap * tanhf(x[idx] * inv_cap);
+}
+
+// One warp per (token, head): y = x / sqrt(mean(x^2) + eps) when `normalise`, times
+// weight[head * weight_head_stride + c] when a weight is given, times sigmoid(gate[t, head, c])
+// when a gate is given. x is [T, heads, width] of type IN; gate rows are `gate_stride` apart.
+template <typename IN, typename T>
+__global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restrict__ weight, int weight_head_stride,
+                                      const T* __restrict__ gate, int gate_stride, T* __restrict__ out,
+                                      int num_tokens, int heads, int width, int normalise, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (warp >= num_tokens * heads) return;
+  const int t = warp / heads, h = warp - t * heads;
+  const IN* xr = x + (size_t)warp * width;
+  float rstd = 1.f;
+  if (normalise) {
+    float ss = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      const float v = to_float(xr[c]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)width + eps);
+  }
+  for (int c = lane; c < width; c += 32) {
+    float v = to_float(xr[c]) * rstd;
+    if (weight) v *= to_float(weight[h * weight_head_stride + c]);
+    if (gate) v *= sigmoidf(to_float(gate[(size_t)t * gate_stride + h * width + c]));
+    out[(size_t)warp * width + c] = from_float<T>(v);
+  }
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+static int blocks_for(size_t total, int threads) {
+  size_t b = (total + threads - 1) / threads;
+  if (b > 148 * 16) b = 148 * 16;
+  return (int)b;
+}
+
+extern "C" int ts_act_mul(const void* gate_up, void* out, int num_tokens, int inter, int activation, int dtype,
+                          cudaStream_t stream) {
+  const size_t total = (size_t)num_tokens * inter;
+  if (total == 0) return 0;
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return TS_ERR_BAD_ARGUMENT;
+  const int b = blocks_for(total, 256);
+#define TS_ACT_CASE(T_, ACT_) \
+  return launch(act_mul_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)gate_up, (T_*)out, inter, total)
+  if (dtype == TS_DTYPE_F32) {
+    if (activation == ACT_SILU) TS_ACT_CASE(float, ACT_SILU);
+    TS_ACT_CASE(float, ACT_GELU_TANH);
+  }
+  if (dtype == TS_DTYPE_BF16) {
+    if (activation == ACT_SILU) TS_ACT_CASE(bf16, ACT_SILU);
+    TS_ACT_CASE(bf16, ACT_GELU_TANH);
+  }
+#undef TS_ACT_CASE
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+extern "C" int ts_softcap(float* x, size_t total, float cap, cudaStream_t stream) {
+  if (total == 0) return 0;
+  if (!(cap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  return launch(softcap_kernel, blocks_for(total, 256), 256, 0, stream, x, cap, 1.f / cap, total);
+}
+
+extern "C" int ts_head_norm_gate(const void* x, int x_is_f32, const void* weight, int weight_head_stride,
+                                 const void* gate, int gate_stride, void* out, int num_tokens, int heads, int width,
+                                 int normalise, float eps, int dtype, cudaStream_t stream) {
+  const size_t warps = (size_t)num_tokens * heads;
+  if (warps == 0) return 0;
+  const int threads = 128;
+  const int b = (int)((warps * 32 + threads - 1) / threads);
+  if (dtype == TS_DTYPE_F32)
+    return launch(head_norm_gate_kernel<float, float>, b, threads, 0, stream, (const float*)x, (const float*)weight,
+                  weight_head_stride, (const float*)gate, gate_stride, (float*)out, num_tokens, heads, width, normalise, eps);
+  if (dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+  if (x_is_f32)
+    return launch(head_norm_gate_kernel<float, bf16>, b, threads, 0, stream, (const float*)x, (const bf16*)weight,
+                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps);
+  return launch(head_norm_gate_kernel<bf16, bf16>, b, threads, 0, stream, (const bf16*)x, (const bf16*)weight,
+                weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps);
+}

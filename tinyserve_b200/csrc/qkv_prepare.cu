@@ -1,0 +1,103 @@
+// Queries, keys and values on their way to attention when keys and values may have different
+// head sizes: per (token, head) an optional RMSNorm over the head (plain weight), an optional
+// rotation of the first `rotary_dim` elements (element i pairs with i + rotary_dim / 2), then
+// queries go to q_out [T, heads, d], keys to k_cache [pages, kv_heads, page_size, d] and values,
+// unchanged, to v_cache [pages, kv_heads, page_size, dv] at the token's slot. q, k and v are read
+// from rows with strides of their own, so they may be parts of one merged projection. All
+// arithmetic is 32-bit and the result is rounded once.
+#define TS_PDL_CLASS PDL_ELEMENTWISE
+#include "common.cuh"
+
+namespace ts {
+
+template <typename T>
+__device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const T* __restrict__ w, float eps,
+                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                 int rotary_dim, int d, T* __restrict__ dst, int lane) {
+  float rstd = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float v = to_float(x[i]);
+      ss = fmaf(v, v, ss);
+    }
+    rstd = rsqrtf(warp_sum(ss) / (float)d + eps);
+  }
+  const int half = rotary_dim >> 1;
+  for (int i = lane; i < d; i += 32) {
+    float y = to_float(x[i]) * rstd;
+    if (w) y *= to_float(w[i]);
+    if (i < rotary_dim) {
+      const int p = i < half ? i + half : i - half;
+      float yp = to_float(x[p]) * rstd;
+      if (w) yp *= to_float(w[p]);
+      const int f = i < half ? i : i - half;
+      const float c = cos_t[f], s = sin_t[f];
+      y = i < half ? y * c - yp * s : y * c + yp * s;
+    }
+    dst[i] = from_float<T>(y);
+  }
+}
+
+template <typename T>
+__global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in, int k_stride,
+                                   const T* __restrict__ v_in, int v_stride, const T* __restrict__ q_w,
+                                   const T* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
+                                   const float* __restrict__ sin_tab, int rotary_dim, const int* __restrict__ slots,
+                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens,
+                                   int heads, int kv_heads, int d, int dv, T* __restrict__ q_out) {
+  pdl_trigger();
+  pdl_wait();
+  const int jobs = heads + (k_in ? 2 * kv_heads : 0);
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long long)num_tokens * jobs) return;
+  const int t = (int)(warp / jobs), job = (int)(warp - (long long)t * jobs);
+  const float* cos_t = rotary_dim ? cos_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
+  const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
+  if (job < heads) {
+    norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_w, eps, cos_t, sin_t, rotary_dim, d,
+                     q_out + ((size_t)t * heads + job) * d, lane);
+    return;
+  }
+  const int slot = slots[t];
+  const int page = slot / page_size, off = slot - page * page_size;
+  if (job < heads + kv_heads) {
+    const int g = job - heads;
+    norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_w, eps, cos_t, sin_t, rotary_dim, d,
+                     k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane);
+    return;
+  }
+  const int g = job - heads - kv_heads;
+  const T* src = v_in + (size_t)t * v_stride + g * dv;
+  T* dst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dv;
+  for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, int k_stride, const void* v_in,
+                              int v_stride, const void* q_w, const void* k_w, float eps, const float* cos_tab,
+                              const float* sin_tab, int rotary_dim, const int* slots, void* k_cache, void* v_cache,
+                              int page_size, int num_tokens, int heads, int kv_heads, int d, int dv, void* q_out,
+                              int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && (!cos_tab || !sin_tab))) return TS_ERR_BAD_ARGUMENT;
+  if (k_in && (!v_in || !slots || !k_cache || !v_cache || page_size <= 0)) return TS_ERR_BAD_ARGUMENT;
+  const long long warps = (long long)num_tokens * (heads + (k_in ? 2 * kv_heads : 0));
+  const int threads = 128;
+  const int blocks = (int)((warps * 32 + threads - 1) / threads);
+  if (dtype == TS_DTYPE_F32)
+    return launch(qkv_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)q_in, q_stride, (const float*)k_in,
+                  k_stride, (const float*)v_in, v_stride, (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab,
+                  rotary_dim, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
+                  (float*)q_out);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(qkv_prepare_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)q_in, q_stride, (const bf16*)k_in,
+                  k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab,
+                  rotary_dim, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
+                  (bf16*)q_out);
+  return TS_ERR_BAD_ARGUMENT;
+}

@@ -34,7 +34,17 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "ts_qk_norm_rope_write": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ts_paged_attention_simt": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                _f, _i, _i, _vp, _vp, _i, _vp],
+                                _f, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
+    "ts_hc_mix_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "ts_hc_collapse": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ts_act_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
+    "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "ts_mlstm_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ts_causal_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "ts_qkv_prepare": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                       _vp, _i, _vp],
     "ts_prefill_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ts_decode_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                 _vp, _vp],
@@ -355,28 +365,38 @@ def choose_splits(ctas: int, slots: int, most: int, cluster: bool = False) -> in
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
-                    block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor) -> None:
+                    block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor,
+                    sinks: torch.Tensor | None = None) -> None:
     """Causal attention of this step's queries over each request's cached keys and values.
 
-    ``q`` ``[T, Hq, D]`` dt; caches ``[pages, Hkv, page_size, D]`` dt; ``block_tables``
-    ``[B, W]`` int32; ``ctx`` supplies ``cu_query_lens``, ``context_lens_dev``, the lists of
-    decoding and prefilling requests and the step's maxima. ``window`` 0 means all earlier
-    positions. ``out`` ``[T, Hq * D]`` dt."""
+    ``q`` ``[T, Hq, D]`` dt; key cache ``[pages, Hkv, page_size, D]`` dt, value cache the same
+    with a head size ``Dv`` of its own; ``block_tables`` ``[B, W]`` int32; ``ctx`` supplies
+    ``cu_query_lens``, ``context_lens_dev``, the lists of decoding and prefilling requests and the
+    step's maxima. ``window`` 0 means all earlier positions. ``sinks`` (float32 ``[Hq]``,
+    optional): a logit per head that joins the softmax's denominator, unscaled, without a value.
+    ``out`` ``[T, Hq * Dv]`` dt."""
     t, hq, d = q.shape
     hkv = k_cache.shape[1]
+    dv = v_cache.shape[3]
     dt = q.dtype
     if k_cache.dtype != dt or v_cache.dtype != dt or out.dtype != dt:
         raise KernelError("paged_attention: dtype mismatch")
-    if tuple(k_cache.shape[1:]) != (hkv, page_size, d) or k_cache.shape != v_cache.shape:
+    if tuple(k_cache.shape[1:]) != (hkv, page_size, d) or tuple(v_cache.shape[:3]) != tuple(k_cache.shape[:3]):
         raise KernelError("paged_attention: cache layout must be [pages, kv_heads, page_size, head_dim]")
-    if out.numel() != t * hq * d or hq % hkv:
+    if out.numel() != t * hq * dv or hq % hkv:
         raise KernelError("paged_attention: out shape or head grouping")
-    if d % 16 or d > 256:
-        raise KernelError(f"paged_attention: head_dim={d} must be a multiple of 16 up to 256")
+    if d % 16 or d > 256 or dv % 16 or dv > 256:
+        raise KernelError(f"paged_attention: head sizes {d}/{dv} must be multiples of 16 up to 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("paged_attention: block_tables must be [requests, width]")
+    if sinks is not None and (sinks.shape != (hq,) or sinks.dtype != torch.float32):
+        raise KernelError("paged_attention: sinks must be float32, one per query head")
     _check_indices("paged_attention", block_tables, ctx, page_size, k_cache.shape[0])
     num_prefill = ctx.num_prefill
+    if sinks is not None or dv != d:
+        # the CUDA-core kernels know sink logits and a value head size of its own
+        _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, sinks, num_prefill)
+        return
     tma_ok = (dt == torch.bfloat16 and d in (64, 128) and (page_size == 8 or page_size % 16 == 0)
               and k_cache.shape[0] * hkv * page_size < 2 ** 31)
     if num_prefill and dt == torch.bfloat16 and d <= 128:
@@ -439,8 +459,16 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                 _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), *common),
                 "decode_attention_mma")
         return
+    _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, None, num_prefill)
+
+
+def _paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
+                          block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor,
+                          sinks: torch.Tensor | None, num_prefill: int) -> None:
+    t, hq, d = q.shape
+    hkv, dv, dt = k_cache.shape[1], v_cache.shape[3], q.dtype
     splits, part_acc, part_ml = 1, None, None
-    if ctx.num_decode:
+    if ctx.num_decode and dv == d:
         splits = decode_splits(ctx.num_decode, hkv, hq // hkv, ctx.max_context_len)
         if splits > 1:
             part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)
@@ -453,7 +481,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
         _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
         hq, hkv, d, page_size, float(scale), int(window), splits,
-        _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention",
+        _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _opt(sinks, "sinks", torch.float32), dv,
+        _code(dt), _stream()), "paged_attention",
         kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0))
 
 
@@ -943,6 +972,202 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("gemm_simt: shape or dtype mismatch")
     _check(_fn("ts_gemm_simt")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _code(x.dtype),
                                _code(out.dtype), _stream()), "gemm_simt")
+
+
+# ------------------------------------------------------------- hyper-connections
+def hc_mix_norm(lanes: torch.Tensor, fresh: torch.Tensor | None, delta: torch.Tensor | None,
+                mix_prev: torch.Tensor | None, out_prev: torch.Tensor | None, in_next: torch.Tensor,
+                norm_weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """The residual stream as ``S`` lanes ``lanes [S, T, h]`` float32. In one pass per row: with
+    ``fresh`` ``[T, h]`` every lane becomes that row; else with a pending sub-layer output
+    ``delta`` ``[T, h]`` dt the lanes are rebuilt, ``x_t <- sum_s mix_prev[s, t] x_s + out_prev[t] delta``;
+    then ``u = sum_s in_next[s] x_s`` and ``out = dt(u / sqrt(mean(u^2) + eps) * norm_weight)``."""
+    s_, t, h = lanes.shape
+    dt = out.dtype
+    if tuple(out.shape) != (t, h) or norm_weight.shape != (h,) or in_next.shape != (s_,):
+        raise KernelError("hc_mix_norm: shape mismatch")
+    if delta is not None and (mix_prev is None or out_prev is None or tuple(mix_prev.shape) != (s_, s_)
+                              or out_prev.shape != (s_,) or tuple(delta.shape) != (t, h)):
+        raise KernelError("hc_mix_norm: a pending output needs its mix [S, S] and out [S]")
+    if fresh is not None and (delta is not None or tuple(fresh.shape) != (t, h)):
+        raise KernelError("hc_mix_norm: fresh lanes take no pending output")
+    _check(_fn("ts_hc_mix_norm")(
+        _dev(lanes, "lanes", torch.float32), _opt(fresh, "fresh", torch.float32), _opt(delta, "delta", dt),
+        _opt(mix_prev, "mix_prev", torch.float32), _opt(out_prev, "out_prev", torch.float32),
+        _dev(in_next, "in_next", torch.float32), _dev(norm_weight, "norm_weight", dt), _dev(out, "out"),
+        s_, t, h, float(eps), _code(dt), _stream()), "hc_mix_norm")
+
+
+def hc_collapse(lanes: torch.Tensor, fresh: torch.Tensor | None, delta: torch.Tensor | None,
+                mix_prev: torch.Tensor | None, out_prev: torch.Tensor | None, rows: torch.Tensor | None,
+                out: torch.Tensor) -> None:
+    """``out[r] = sum_t x_t`` (float32 ``[R, h]``) at the rows ``rows`` (int32; all rows if
+    ``None``), after the pending rebuild of ``hc_mix_norm``; the lanes are left as they are."""
+    s_, t, h = lanes.shape
+    r = out.shape[0]
+    dt = delta.dtype if delta is not None else torch.float32
+    if out.shape[1] != h or (rows is None and r != t) or (rows is not None and rows.shape != (r,)):
+        raise KernelError("hc_collapse: shape mismatch")
+    if delta is not None and (mix_prev is None or out_prev is None):
+        raise KernelError("hc_collapse: a pending output needs its mix and out")
+    _check(_fn("ts_hc_collapse")(
+        _dev(lanes, "lanes", torch.float32), _opt(fresh, "fresh", torch.float32), _opt(delta, "delta"),
+        _opt(mix_prev, "mix_prev", torch.float32), _opt(out_prev, "out_prev", torch.float32),
+        _opt(rows, "rows", torch.int32), _dev(out, "out", torch.float32), s_, t, r, h, _code(dt), _stream()),
+        "hc_collapse")
+
+
+# --------------------------------------------------------------------------- gates
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """``out[t, j] = dt(act(gate_up[t, j]) * gate_up[t, I + j])`` in 32-bit, rounded once;
+    ``activation``: "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    t, inter = out.shape
+    if gate_up.shape != (t, 2 * inter) or gate_up.dtype != out.dtype or activation not in ACTIVATIONS:
+        raise KernelError("act_mul: shape, dtype or activation")
+    _check(_fn("ts_act_mul")(_dev(gate_up, "gate_up"), _dev(out, "out"), t, inter, ACTIVATIONS[activation],
+                             _code(out.dtype), _stream()), "act_mul")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """In place on float32: ``x <- cap * tanh(x / cap)``."""
+    _check(_fn("ts_softcap")(_dev(logits, "logits", torch.float32), logits.numel(), float(cap), _stream()), "softcap")
+
+
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head: bool, gate: torch.Tensor | None,
+                   normalise: bool, eps: float, out: torch.Tensor) -> None:
+    """Per (token, head) of ``x [T, H, w]`` (float32 or dt): divide by the root mean square over
+    ``w`` (``normalise``), multiply by ``weight`` (``[H * w]`` when ``weight_per_head`` else ``[w]``
+    shared by the heads) and by ``sigmoid(gate[t, h, :])`` (``gate`` dt, rows of ``H * w`` values,
+    possibly a column slice of a wider matrix); ``out [T, H * w]`` dt."""
+    t, heads, w = x.shape
+    dt = out.dtype
+    if out.numel() != t * heads * w or x.dtype not in (torch.float32, dt):
+        raise KernelError("head_norm_gate: shape or dtype mismatch")
+    if weight is not None and weight.numel() != (heads * w if weight_per_head else w):
+        raise KernelError("head_norm_gate: weight size")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != dt or gate.shape[0] != t or gate.shape[1] != heads * w or gate.stride(1) != 1:
+            raise KernelError("head_norm_gate: gate must be [T, H * w] dt with unit column stride")
+        gate_stride = gate.stride(0)
+    _check(_fn("ts_head_norm_gate")(
+        _dev(x, "x"), int(x.dtype == torch.float32), _opt(weight, "weight", dt), w if weight_per_head else 0,
+        None if gate is None else gate.data_ptr(), gate_stride, _dev(out, "out"), t, heads, w, int(bool(normalise)),
+        float(eps), _code(dt), _stream()), "head_norm_gate")
+
+
+# ---------------------------------------------------------------- recurrent mixers
+SCAN_MAX_KEY_DIM = 256
+SCAN_MAX_TAPS = 8
+
+
+def _state_rows(state: torch.Tensor, width: int, name: str) -> tuple[int, int]:
+    """Address and row stride of per-slot state ``[slots, width]`` float32: whole rows of the
+    slot storage or a column range of them."""
+    if (not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != width
+            or (width > 1 and state.stride(1) != 1)):
+        raise KernelError(f"{name}: state must be float32 [slots, {width}] on the device with unit column stride")
+    return state.data_ptr(), state.stride(0)
+
+
+def mlstm_state_size(heads: int, d: int, dv: int) -> int:
+    """Floats of one request's state: per head ``S [d, dv]`` and, per block of 32 value columns,
+    a copy of the normaliser ``n [d]`` and the running maximum ``m``."""
+    return heads * (d * dv + -(-dv // 32) * (d + 1))
+
+
+def mlstm_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, gate_bias: torch.Tensor,
+               cap: float, q_scale: float, state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int,
+               out: torch.Tensor) -> None:
+    """The mLSTM recurrence over this step's tokens of every request, from and to its state slot.
+    ``qkv [T, *]`` dt holds q, k (``heads * d`` each) and v (``heads * dv``) at the given column
+    offsets; ``gates [T, 2 * heads]`` float32 the pre-activations of the input and forget gates
+    (bias not yet added, ``gate_bias [2 * heads]`` float32); ``state [slots, mlstm_state_size]``
+    float32; ``out [T, heads, dv]`` float32 (before the head norm)."""
+    t = qkv.shape[0]
+    if gates.shape != (t, 2 * heads) or gate_bias.shape != (2 * heads,) or tuple(out.shape) != (t, heads, dv):
+        raise KernelError("mlstm_scan: shape mismatch")
+    if d > SCAN_MAX_KEY_DIM:
+        raise KernelError("mlstm_scan: key size")
+    state_ptr, state_stride = _state_rows(state, mlstm_state_size(heads, d, dv), "mlstm_scan")
+    _check(_fn("ts_mlstm_scan")(
+        _dev(qkv, "qkv"), qkv.shape[1], q_off, k_off, v_off, _dev(gates, "gates", torch.float32),
+        _dev(gate_bias, "gate_bias", torch.float32), float(cap), float(q_scale), state_ptr, state_stride,
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
+        ctx.num_seqs, heads, d, dv, _dev(out, "out", torch.float32), _code(qkv.dtype), _stream()), "mlstm_scan")
+
+
+def delta_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, a: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, beta_pre: torch.Tensor, q_scale: float, state: torch.Tensor, ctx: Any,
+               heads: int, kv_heads: int, d: int, dv: int, out: torch.Tensor) -> None:
+    """The gated delta rule with a decay per key channel over this step's tokens, from and to the
+    state slot. ``qkv [T, *]`` float32 holds q, k (``kv_heads * d``) and v (``heads * dv``) after
+    their convolutions; ``a [T, heads * d]`` float32 the step-size pre-activations, ``dt_bias
+    [heads * d]``, ``a_log [heads]``, ``beta_pre [T, heads]`` float32; ``state [slots, heads * d * dv]``
+    float32; ``out [T, heads, dv]`` float32. q and k are scaled to unit length inside (q also by
+    ``q_scale``); head h reads q/k head ``h // (heads / kv_heads)``."""
+    t = qkv.shape[0]
+    if a.shape != (t, heads * d) or beta_pre.shape != (t, heads) or tuple(out.shape) != (t, heads, dv):
+        raise KernelError("delta_scan: shape mismatch")
+    if dt_bias.shape != (heads * d,) or a_log.shape != (heads,) or d > SCAN_MAX_KEY_DIM:
+        raise KernelError("delta_scan: parameter or key size")
+    state_ptr, state_stride = _state_rows(state, heads * d * dv, "delta_scan")
+    _check(_fn("ts_delta_scan")(
+        _dev(qkv, "qkv", torch.float32), qkv.shape[1], q_off, k_off, v_off, _dev(a, "a", torch.float32),
+        _dev(dt_bias, "dt_bias", torch.float32), _dev(a_log, "a_log", torch.float32),
+        _dev(beta_pre, "beta_pre", torch.float32), float(q_scale), state_ptr, state_stride,
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
+        ctx.num_seqs, heads, kv_heads, d, dv, _dev(out, "out", torch.float32), _stream()), "delta_scan")
+
+
+def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, ctx: Any, out: torch.Tensor) -> None:
+    """``out[t, c] = silu(sum_k taps[c, k] * in[t - (K - 1 - k), c])`` (float32) per request, where
+    tokens before this step come from ``state [slots, (K - 1) * C]`` float32 (zero at a request's
+    start); afterwards the state holds the request's last ``K - 1`` inputs. ``x [T, C]`` dt, ``taps [C, K]`` dt."""
+    t, c = x.shape
+    k = taps.shape[1]
+    if taps.shape[0] != c or tuple(out.shape) != (t, c) or taps.dtype != x.dtype:
+        raise KernelError("causal_conv_silu: shape or dtype mismatch")
+    state_ptr, state_stride = _state_rows(state, (k - 1) * c, "causal_conv_silu")
+    _check(_fn("ts_causal_conv_silu")(
+        _dev(x, "x"), c, _dev(taps, "taps"), state_ptr, state_stride,
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
+        ctx.num_seqs, t, c, k, _dev(out, "out", torch.float32), _code(x.dtype), _stream()), "causal_conv_silu",
+        kernels=2 if k > 1 else 1)
+
+
+def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tensor | None, q_weight: torch.Tensor | None,
+                k_weight: torch.Tensor | None, eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None,
+                rotary_dim: int, slots: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+                page_size: int, heads: int, kv_heads: int, d: int, dv: int, q_out: torch.Tensor) -> None:
+    """Per (token, head): optional RMSNorm over the head with a plain weight, rotation of the first
+    ``rotary_dim`` elements (i pairs with i + rotary_dim / 2); queries to ``q_out [T, heads, d]``,
+    keys and (unchanged) values to the caches at the tokens' slots (when ``k_in`` is given).
+    ``q_in``/``k_in``/``v_in`` are 2-D dt with unit column stride (column slices of a merged
+    projection are fine); the value head size ``dv`` may differ from ``d``."""
+    t = q_out.shape[0]
+    dt = q_out.dtype
+    for name, x, width in (("q_in", q_in, heads * d), ("k_in", k_in, kv_heads * d), ("v_in", v_in, kv_heads * dv)):
+        if x is not None and (x.dtype != dt or x.shape != (t, width) or x.stride(1) != 1 or not x.is_cuda):
+            raise KernelError(f"qkv_prepare: {name} must be [T, {width}] {dt} with unit column stride on the device")
+    if tuple(q_out.shape) != (t, heads, d) or (k_in is None) != (v_in is None):
+        raise KernelError("qkv_prepare: q_out shape, or keys without values")
+    if k_in is not None:
+        if tuple(k_cache.shape[1:]) != (kv_heads, page_size, d) or tuple(v_cache.shape[1:]) != (kv_heads, page_size, dv):
+            raise KernelError("qkv_prepare: cache layout")
+        _check_indices("qkv_prepare", None, None, page_size, k_cache.shape[0], slots)
+    if rotary_dim and (cos is None or tuple(cos.shape) != (t, rotary_dim // 2) or tuple(sin.shape) != tuple(cos.shape)):
+        raise KernelError("qkv_prepare: rotary tables missing or of the wrong shape")
+    _check(_fn("ts_qkv_prepare")(
+        q_in.data_ptr(), q_in.stride(0), None if k_in is None else k_in.data_ptr(), 0 if k_in is None else k_in.stride(0),
+        None if v_in is None else v_in.data_ptr(), 0 if v_in is None else v_in.stride(0),
+        _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt), float(eps),
+        _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
+        _opt(slots, "slots", torch.int32), _opt(k_cache, "k_cache", dt), _opt(v_cache, "v_cache", dt), page_size, t,
+        heads, kv_heads, d, dv, _dev(q_out, "q_out"), _code(dt), _stream()), "qkv_prepare")
 
 
 # --------------------------------------------------------------------- sampling

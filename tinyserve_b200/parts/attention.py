@@ -17,8 +17,8 @@ from typing import Any, Mapping
 import torch
 
 from ..kernels import ops
-from .base import (EVERY_STEP, KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, StepContext, TensorSpec, project,
-                   project_to_stream, register_mixer)
+from .base import (EVERY_STEP, KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, SplitKVNeed, StepContext,
+                   TensorSpec, project, project_to_stream, register_mixer)
 
 
 class GQAAttention(Mixer):
@@ -126,4 +126,103 @@ class GQAAttention(Mixer):
         return project_to_stream(attn, self.w_o, stream, ctx)
 
 
+class GatedSinkAttention(Mixer):
+    """Grouped-query attention with a sink logit per head and a sigmoid output gate.
+
+    ``q = W_q h`` (``num_heads x key_dim``), ``k = W_k h`` (``num_kv_heads x key_dim``),
+    ``v = W_v h`` (``num_kv_heads x value_dim``: values may have a head size of their own), no
+    biases; optional RMSNorm of q and k per head (plain weights shared by the heads) before the
+    rotation that the layer's position encoding asks for; scores ``scale * q . k``, causal; the
+    softmax's denominator also holds ``exp(sink_h)``, which has no key and no value; the
+    concatenated heads are multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``. With
+    ``own_kv=False`` the layer has no key/value tensors and only ever runs as a call that reads
+    another call's cache. ``names`` maps the roles "q", "k", "v", "gate", "out", "q_norm",
+    "k_norm", "sink" to tensor names after the prefix.
+
+    One product makes q, k, v and the gate's pre-activation; norm, rotation and the cache write are
+    one kernel; attention runs over the pages; the gate is applied in 32-bit and rounded once.
+    """
+
+    recordable = EVERY_STEP
+    _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm", "sink": "sink"}
+
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                 scale: float, qk_norm: bool = True, qk_norm_eps: float = 1e-6, sink: bool = True,
+                 own_kv: bool = True, names: Mapping[str, str] | None = None) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        for what, size in (("key_dim", key_dim), ("value_dim", value_dim)):
+            if size <= 0 or size % 16 or size > 256:
+                raise ValueError(f"{what}={size}: the attention kernels take head sizes in steps of 16 up to 256")
+        self.prefix, self.h = prefix, int(hidden_size)
+        self.heads, self.groups, self.d, self.dv = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
+        self.scale, self.qk_norm, self.eps = float(scale), bool(qk_norm), float(qk_norm_eps)
+        self.has_sink, self.own_kv = bool(sink), bool(own_kv)
+        self.names = {**self._NAMES, **(names or {})}
+        self.q_norm_w = self.k_norm_w = self.sink = None
+
+    def cache_need(self) -> "KVNeed | SplitKVNeed":
+        if self.d == self.dv:
+            return KVNeed(self.groups, self.d, None)
+        return SplitKVNeed(self.groups, self.d, self.dv, None)
+
+    def _widths(self) -> tuple[int, int, int, int]:
+        return self.heads * self.d, self.groups * self.d, self.groups * self.dv, self.heads * self.dv
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, n, h = prefix + self.prefix, self.names, self.h
+        q, k, v, g = self._widths()
+        if self.own_kv:
+            specs = [TensorSpec(p + "qkvg", (q + k + v + g, h), merged_from=tuple(p + n[r] for r in ("q", "k", "v", "gate")),
+                                merged_rows=(q, k, v, g))]
+        else:
+            specs = [TensorSpec(p + "qg", (q + g, h), merged_from=(p + n["q"], p + n["gate"]), merged_rows=(q, g))]
+        specs.append(TensorSpec(p + n["out"], (h, g)))
+        if self.qk_norm:
+            specs.append(TensorSpec(p + n["q_norm"], (self.d,), init="one_plus_normal"))
+            if self.own_kv:
+                specs.append(TensorSpec(p + n["k_norm"], (self.d,), init="one_plus_normal"))
+        if self.has_sink:
+            specs.append(TensorSpec(p + n["sink"], (self.heads,), std=1.0))
+        return specs
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = prefix + self.prefix, self.names
+        self.w_in = tensors[p + ("qkvg" if self.own_kv else "qg")]
+        self.w_o = tensors[p + n["out"]]
+        if self.qk_norm:
+            self.q_norm_w = tensors[p + n["q_norm"]]
+            self.k_norm_w = tensors[p + n["k_norm"]] if self.own_kv else None
+        if self.has_sink:
+            self.sink = tensors[p + n["sink"]].float().contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheEntry, writes_cache: bool, position: Any) -> torch.Tensor:
+        if writes_cache != self.own_kv:
+            raise RuntimeError("a layer without key/value tensors must read another call's cache, and one with them writes its own")
+        t, arena = x.shape[0], ctx.arena
+        group = ctx.kv[cache.group]
+        q, k, v, g = self._widths()
+        proj = arena.take((t, self.w_in.shape[0]), ctx.dtype)
+        ops.gemm(x, self.w_in, proj)
+        rot = None if position is None else position.qk_rotation()
+        if rot is not None and rot.interleaved:
+            raise NotImplementedError("this mixer rotates pairs (i, i + rotary_dim / 2) only")
+        queries = arena.take((t, self.heads, self.d), ctx.dtype)
+        ops.qkv_prepare(proj[:, :q], proj[:, q: q + k] if writes_cache else None,
+                        proj[:, q + k: q + k + v] if writes_cache else None, self.q_norm_w, self.k_norm_w, self.eps,
+                        None if rot is None else rot.cos, None if rot is None else rot.sin,
+                        0 if rot is None else rot.rotary_dim, group.slots if writes_cache else None,
+                        cache.k if writes_cache else None, cache.v if writes_cache else None, cache.page_size,
+                        self.heads, self.groups, self.d, self.dv, queries)
+        attn = arena.take((t, g), ctx.dtype)
+        ops.paged_attention(queries, cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale, 0, attn,
+                            sinks=self.sink)
+        gated = arena.take((t, g), ctx.dtype)
+        ops.head_norm_gate(attn.view(t, self.heads, self.dv), None, False, proj[:, proj.shape[1] - g:], False, 0.0, gated)
+        out = arena.take((t, self.h), ctx.dtype)
+        ops.gemm(gated, self.w_o, out)
+        return out
+
+
 register_mixer("gqa_attention", GQAAttention)
+register_mixer("gated_sink_attention", GatedSinkAttention)

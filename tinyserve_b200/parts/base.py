@@ -42,6 +42,8 @@ class TensorSpec:
 
     ``merged_from`` lists checkpoint tensors whose rows, stacked in that order, make this
     tensor; a checkpoint may store either the merged tensor or all of its sources.
+    A dimension of ``-1`` in ``shape`` is taken from the checkpoint (a size that no configuration
+    key gives, such as the rank of a low-rank pair); such a spec cannot be drawn at random.
     ``init`` names the law of the random-weights mode: ``"normal"`` is N(0, std),
     ``"one_plus_normal"`` is 1 + N(0, std). ``keep_32bit`` marks tensors that stay 32-bit
     when the checkpoint stores them so, whatever the run's dtype; integer tables are always
@@ -123,6 +125,39 @@ class KVNeed(PagedNeed):
 
 
 @dataclass(frozen=True)
+class SplitKVNeed(PagedNeed):
+    """Pages of keys and values whose heads differ in size: keys ``num_kv_heads x key_dim``, values
+    ``num_kv_heads x value_dim`` per token. The group's storage is one flat run of elements; each
+    call owns a stretch of it, keys ``[page, kv_head, offset, key_dim]`` first, then values
+    ``[page, kv_head, offset, value_dim]``."""
+
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: int | None = None
+
+    def bytes_per_token(self, element_size: int) -> int:
+        return self.num_kv_heads * (self.key_dim + self.value_dim) * element_size
+
+    def _per_call(self, num_pages: int, page_size: int) -> tuple[int, int]:
+        rows = num_pages * self.num_kv_heads * page_size
+        return rows * self.key_dim, rows * self.value_dim
+
+    def allocate(self, num_calls, num_pages, page_size, dtype, device):
+        nk, nv = self._per_call(num_pages, page_size)
+        return torch.zeros((num_calls, nk + nv), dtype=dtype, device=device)
+
+    def entry(self, storage, call_in_group, group, page_size):
+        per_page = self.num_kv_heads * page_size * (self.key_dim + self.value_dim)
+        num_pages = storage.shape[1] // per_page
+        nk, _ = self._per_call(num_pages, page_size)
+        mine = storage[call_in_group]
+        k = mine[:nk].view(num_pages, self.num_kv_heads, page_size, self.key_dim)
+        v = mine[nk:].view(num_pages, self.num_kv_heads, page_size, self.value_dim)
+        return KVCacheEntry(group, k, v, page_size)
+
+
+@dataclass(frozen=True)
 class StateNeed(SlotNeed):
     """A slot of fixed size per request: ``shape`` elements of ``dtype``."""
 
@@ -139,7 +174,8 @@ class StateNeed(SlotNeed):
 @dataclass
 class KVCacheEntry:
     """The cache one call of a layer owns: ``k``/``v`` are ``[pages, kv_heads, page_size,
-    head_dim]``; ``group`` finds this call's block tables and slots in the step context."""
+    head_dim]`` (the last size may differ between the two under a ``SplitKVNeed``); ``group``
+    finds this call's block tables and slots in the step context."""
 
     group: int
     k: torch.Tensor
@@ -206,13 +242,20 @@ class ResidualStream:
     last sub-layer's output in the model dtype, not yet added. ``sumsq``, when set, holds the
     sums of squares of the rows of ``resid`` in parts, left by the product that last added to the
     stream (``ops.gemm_to_stream``) together with ``resid16``, a copy of the stream in the model
-    dtype; both are valid only while ``delta`` is None."""
+    dtype; both are valid only while ``delta`` is None.
 
-    __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf")
+    A model with hyper-connections keeps several copies of the stream: ``lanes`` is 32-bit
+    ``[S, T, hidden]`` (``None`` until the first sub-layer makes them from ``resid``, the embedding
+    output), and ``connection`` holds the ``(mix [S, S], out [S])`` weights with which the pending
+    ``delta`` enters the lanes (``parts.hyper``)."""
+
+    __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf", "lanes", "connection")
 
     def __init__(self, resid: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.resid = resid
         self.delta = delta
+        self.lanes: torch.Tensor | None = None
+        self.connection: tuple[torch.Tensor, torch.Tensor] | None = None
         self.sumsq: torch.Tensor | None = None
         self.resid16: torch.Tensor | None = None
         self._sumsq_buf: torch.Tensor | None = None

@@ -37,7 +37,11 @@ class LMHead(Part):
     recordable = EVERY_STEP
 
     def __init__(self, name: str, tied: bool, vocab_size: int, hidden_size: int,
-                 ignored_when_tied: str | None = None) -> None:
+                 ignored_when_tied: str | None = None, softcap: float | None = None) -> None:
+        # softcap: logits <- softcap * tanh(logits / softcap) after the product (None: no cap)
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"softcap must be positive or None, got {softcap}")
+        self.softcap = None if softcap is None else float(softcap)
         self.name, self.tied = name, bool(tied)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.ignored_when_tied = ignored_when_tied
@@ -58,6 +62,8 @@ class LMHead(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``x [R, hidden]`` in the model dtype -> ``out [R, vocab]`` float32."""
         ops.gemm(x, self.weight, out)
+        if self.softcap is not None:
+            ops.softcap(out, self.softcap)
         return out
 
 

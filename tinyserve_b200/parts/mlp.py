@@ -53,4 +53,48 @@ class SwiGLU(FeedForward):
         return project_to_stream(act, self.w_down, stream, ctx)
 
 
+class GatedMLP(FeedForward):
+    """``y = (act(x Wgate^T) * (x Wup^T)) Wdown^T`` with a choice of activation ("silu",
+    "gelu_tanh": ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``) and of tensor names
+    (``names``: role "gate" / "up" / "down" -> name after the prefix). Gate and up come from one
+    product with the merged matrix; the activation and the product of the halves are 32-bit and
+    rounded once."""
+
+    recordable = EVERY_STEP
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: "Mapping[str, str] | None" = None) -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.prefix, self.activation = prefix, activation
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, h, i, n = prefix + self.prefix, self.hidden_size, self.intermediate_size, self.names
+        return [TensorSpec(p + n["gate"] + "+" + n["up"], (2 * i, h), merged_from=(p + n["gate"], p + n["up"]),
+                           merged_rows=(i, i)),
+                TensorSpec(p + n["down"], (h, i))]
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = prefix + self.prefix, self.names
+        self.w_gate_up = tensors[p + n["gate"] + "+" + n["up"]]
+        self.w_down = tensors[p + n["down"]]
+
+    def streamed_weights(self) -> list[torch.Tensor]:
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        t = x.shape[0]
+        both = ctx.arena.take((t, 2 * self.intermediate_size), ctx.dtype)
+        ops.gemm(x, self.w_gate_up, both)
+        act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
+        ops.act_mul(both, act, self.activation)
+        out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
+        ops.gemm(act, self.w_down, out)
+        return out
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("gated_mlp", GatedMLP)

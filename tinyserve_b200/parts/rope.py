@@ -9,6 +9,7 @@ former) is applied by the mixer's fused kernel, which receives these tables.
 
 from __future__ import annotations
 
+import math
 from typing import Any
 
 import torch
@@ -19,10 +20,25 @@ from .base import EVERY_STEP, PositionEncoding, Rotation, StepContext, register_
 RotaryTables = Rotation      # the step's position data of a rotary encoding is the rotation itself
 
 
+def scale_by_wavelength(freq: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Frequency scaling by wavelength (the Llama 3.1 rule), in float64: with wavelength
+    ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes ``f / factor`` where
+    ``l > original / low``, and in between is ``(1 - s) f / factor + s f`` with
+    ``s = (original / l - low) / (high - low)``."""
+    if not (factor > 0 and high > low and original > 0):
+        raise ValueError(f"rotary scaling needs factor > 0, high > low, original > 0; got {factor}, {low}, {high}, {original}")
+    wavelength = 2.0 * math.pi / freq
+    s = (original / wavelength - low) / (high - low)
+    blended = (1.0 - s) * freq / factor + s * freq
+    out = torch.where(wavelength > original / low, freq / factor, blended)
+    return torch.where(wavelength < original / high, freq, out)
+
+
 class RotaryEncoding(PositionEncoding):
     recordable = EVERY_STEP
 
-    def __init__(self, head_dim: int, rotary_dim: int, theta: float, pairing: str = "half") -> None:
+    def __init__(self, head_dim: int, rotary_dim: int, theta: float, pairing: str = "half",
+                 scaling: "dict[str, float] | None" = None) -> None:
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim={rotary_dim} must be even and at most head_dim={head_dim}")
         if pairing not in ("half", "interleaved"):
@@ -31,10 +47,14 @@ class RotaryEncoding(PositionEncoding):
         self.theta, self.pairing = float(theta), pairing
         two_i = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
         self._inv_freq_host = self.theta ** (-two_i / self.rotary_dim)
+        self.scaling = None
+        if scaling:
+            self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            self._inv_freq_host = scale_by_wavelength(self._inv_freq_host, *self.scaling)
         self._inv_freq: torch.Tensor | None = None
 
     def key(self) -> Any:
-        return ("rope", self.rotary_dim, self.theta, self.pairing)
+        return ("rope", self.rotary_dim, self.theta, self.pairing, self.scaling)
 
     def prepare(self, ctx: StepContext) -> RotaryTables:
         dev = ctx.positions.device

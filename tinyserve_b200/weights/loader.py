@@ -39,6 +39,11 @@ def merge_specs(specs: Iterable[TensorSpec]) -> dict[str, TensorSpec]:
     return out
 
 
+def shape_fits(shape: tuple[int, ...], expected: tuple[int, ...]) -> bool:
+    """Whether a stored shape is what a spec asks for; ``-1`` in the spec takes any size."""
+    return len(shape) == len(expected) and all(e == -1 or e == s for s, e in zip(shape, expected))
+
+
 def checkpoint_names(specs: Mapping[str, TensorSpec]) -> dict[str, tuple[int, ...]]:
     """Names and shapes as a checkpoint conventionally stores them (sources, not merged)."""
     out: dict[str, tuple[int, ...]] = {}
@@ -83,7 +88,7 @@ def load_tensors(model_dir: str | Path, specs: Iterable[TensorSpec], dtype: torc
         if spec.name in present:
             consumed.add(spec.name)
             shape = present[spec.name][1]
-            if shape != spec.shape:
+            if not shape_fits(shape, spec.shape):
                 wrong.append(f"{spec.name}: shape {shape}, expected {spec.shape}")
             plan[spec.name] = (spec.name,)
             continue
@@ -96,7 +101,7 @@ def load_tensors(model_dir: str | Path, specs: Iterable[TensorSpec], dtype: torc
                     continue
                 consumed.add(src)
                 expect = (rows, *spec.shape[1:])
-                if present[src][1] != expect:
+                if not shape_fits(present[src][1], expect):
                     wrong.append(f"{src}: shape {present[src][1]}, expected {expect}")
                     ok = False
             if ok:
@@ -125,7 +130,7 @@ def load_tensors(model_dir: str | Path, specs: Iterable[TensorSpec], dtype: torc
             if len(parts) == 1:
                 t = parts[0].to(device=device, dtype=target)
             else:
-                t = torch.empty(spec.shape, dtype=target, device=device)
+                t = torch.empty((sum(p.shape[0] for p in parts), *parts[0].shape[1:]), dtype=target, device=device)
                 row = 0
                 for part in parts:
                     t[row: row + part.shape[0]] = part.to(device=device, dtype=target)
