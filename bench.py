@@ -553,6 +553,10 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true",
                     help="skip the batch 1 / 64 points, the prefill and the larger models")
     ap.add_argument("--skip-large", action="store_true", help="skip the points of the 8B and 32B sizes")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the headline: prefill and decode throughput of the Fegilix design beside Qwen3 at "
+                         "equal layer sizes (bench_designs.py); with --kernels also each step's time by kernel class")
+    ap.add_argument("--design-sizes", default="", help="with --designs: layer sizes to run, e.g. 1k or 1k,4k (default: all)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU only; --gpus {args.gpus} is not supported")
@@ -569,6 +573,10 @@ def main() -> int:
     pk, pk_src = peaks()
     if args.profile == "gemm":
         return gemm_table()
+    if args.designs:
+        import bench_designs
+
+        return bench_designs.run(args)
     b = Bench(args.model, args.layers, graphs=not args.no_graphs)
     cfg, dev = b.cfg, b.dev
 

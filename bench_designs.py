@@ -1,0 +1,246 @@
+"""``python bench.py --designs``: prefill and decode throughput of the Fegilix design at layer
+sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder, the closest
+existing model, with the same width, attention heads, feed-forward size and number of layers; and
+where each design's step time goes, kernel class by kernel class, with the share of the measured
+peaks each class reaches. The default workload of ``bench.py`` does not come through here.
+
+The Fegilix layers follow the pattern mLSTM, mLSTM, attention + feed-forward, delta rule, mLSTM,
+attention on the third layer's keys and values + feed-forward, with two hyper-connection lanes.
+"""
+
+from __future__ import annotations
+
+import json
+import statistics
+
+from bench import PAGE, Bench, peaks
+
+SIZES = {
+    # width, attention heads, kv heads, head size, feed-forward, recurrent heads
+    "1k": dict(width=1024, heads=16, kv_heads=8, dim=128, ff=3072, rec_heads=8),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, rec_heads=32),
+}
+VOCAB = 32768
+LAYERS = 6
+
+
+def fegilix_config(s: dict) -> dict:
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "rot": {"dims": s["dim"], "base": 1e6}}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    mlstm = {"type": "mlstm", "mlp": None, "mixer": {"heads": s["rec_heads"], "dim": s["dim"], "vdim": s["dim"], "gate_cap": 15.0}}
+    delta = {"type": "channel_delta", "mlp": None,
+             "mixer": {"heads": s["rec_heads"], "kv_heads": max(1, s["rec_heads"] // 2), "dim": s["dim"], "vdim": s["dim"],
+                       "conv": 4, "step_rank": 64, "gate_rank": 64}}
+    return {"architecture": "Fegilix", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "streams": 2,
+            "logit_softcap": 30.0, "max_positions": 8192,
+            "layers": [mlstm, mlstm, {"type": "attention", "mlp": mlp, "mixer": attn}, delta, mlstm,
+                       {"type": "attention", "mlp": mlp, "mixer": {**attn, "kv_from": 2}}]}
+
+
+def qwen3_config(s: dict) -> dict:
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": VOCAB, "hidden_size": s["width"],
+            "intermediate_size": s["ff"], "num_hidden_layers": LAYERS, "num_attention_heads": s["heads"],
+            "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "hidden_act": "silu", "rms_norm_eps": 1e-6,
+            "rope_theta": 1e6, "max_position_embeddings": 8192, "tie_word_embeddings": False}
+
+
+NEW_OPS = ["hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
+           "causal_conv_silu", "qkv_prepare"]
+OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
+           "decode_attention_fused", "gemm", "gemm_swiglu", "gemm_to_stream", "gemm_normed", "sample"]
+
+
+class DesignBench(Bench):
+    def __init__(self, cfg_dict: dict, graphs: bool = True) -> None:
+        import torch
+
+        from tinyserve_b200.config import config_from_dict
+        from tinyserve_b200.model import DecoderModel
+
+        self.torch, self.name = torch, cfg_dict.get("architecture") or cfg_dict["architectures"][0]
+        self.cfg = config_from_dict(cfg_dict)
+        self.dev = torch.device("cuda:0")
+        torch.cuda.set_device(self.dev)
+        self.model = DecoderModel.from_config(self.cfg, seed=0, dtype=torch.bfloat16, device=self.dev)
+        self.graphs = graphs
+        self.gen = torch.Generator().manual_seed(0)
+        self.check_rel, self.checks = 0.0, 0
+
+    def kv_bytes_per_token(self) -> int:
+        return max(super().kv_bytes_per_token(), 1)
+
+    def prefill_ms(self, tokens: int) -> float:
+        from tinyserve_b200.engine.step import StepEntry
+
+        torch = self.torch
+        e = self.new_engine(1, tokens + 8)
+        toks = self.prompts([tokens])[0]
+        times = []
+        for it in range(3 + 5):
+            req = e.cache.new_request()
+            e.cache.append(req, tokens)
+            torch.cuda.synchronize()
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record()
+            e.runner.step([StepEntry(req, toks)])
+            e_.record()
+            torch.cuda.synchronize()
+            e.cache.free(req)
+            if it >= 3:
+                times.append(s_.elapsed_time(e_))
+        return statistics.median(times)
+
+    def op_table(self, batch: int, prompt_len: int, pk: dict, prefill_tokens: int = 0) -> dict:
+        """Device time of a step by ``ops`` function (event pairs around every call, the step queued
+        behind a spin kernel, launch overlap off; median of three steps), with the bytes a call must
+        move and its multiply-adds where they are what bounds it."""
+        from tinyserve_b200.engine.step import StepEntry
+        from tinyserve_b200.kernels import ops
+
+        torch = self.torch
+        saved, self.graphs = self.graphs, False
+        if prefill_tokens:
+            e = self.new_engine(1, prefill_tokens + 8, run_ahead=False)
+            prompt, reqs = self.prompts([prefill_tokens])[0], []
+        else:
+            e = self.prefilled(batch, prompt_len, 16, run_ahead=False)
+            reqs = list(e.requests.values())
+        self.graphs = saved
+        e.runner.tune_launch_overlap = False
+        ops.set_programmatic_launch(0)
+        records: list = []
+
+        def nbytes(*ts) -> float:
+            return float(sum(t.numel() * t.element_size() for t in ts if isinstance(t, torch.Tensor)))
+
+        def work(name: str, a: tuple, k: dict) -> tuple[float, float]:
+            """(bytes, flops) of one call."""
+            if name in ("gemm", "gemm_swiglu", "gemm_to_stream"):
+                return nbytes(a[0], a[1], a[2]), 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "gemm_normed":
+                return nbytes(a[0], a[4], a[5]), 2.0 * a[0].shape[0] * a[4].shape[0] * a[4].shape[1]
+            if name in ("paged_attention", "decode_attention_fused"):
+                kc, vc = (a[1], a[2]) if name == "paged_attention" else (a[7], a[8])
+                ctx = a[5] if name == "paged_attention" else a[11]
+                heads = a[0].shape[1] if name == "paged_attention" else a[14]
+                pairs = sum(n * (c - n) + n * (n + 1) / 2 for n, c in zip(ctx.query_lens, ctx.context_lens))
+                return (float(sum(ctx.context_lens)) * kc.shape[1] * (kc.shape[3] + vc.shape[3]) * kc.element_size(),
+                        2.0 * heads * (kc.shape[3] + vc.shape[3]) * pairs)
+            if name in ("qk_norm_rope_write", "qkv_prepare"):
+                return 2.0 * nbytes(a[0]), 0.0
+            if name == "embed":
+                return nbytes(a[0], a[2]) + a[0].numel() * a[1].shape[1] * a[1].element_size(), 0.0
+            if name == "mlstm_scan":          # state in and out, the rows read, the read-out written; 6 flops per state element and token
+                ctx, heads, d, dv = a[9], a[10], a[11], a[12]
+                return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[4], a[13]), 6.0 * a[0].shape[0] * heads * d * dv)
+            if name == "delta_scan":          # 8 flops per state element and token
+                ctx, heads, d, dv = a[10], a[11], a[13], a[14]
+                return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[4], a[7], a[15]), 8.0 * a[0].shape[0] * heads * d * dv)
+            if name == "causal_conv_silu":
+                return nbytes(a[0], a[4]), 0.0
+            if name == "hc_mix_norm":         # the lanes read and written, the pending output, the result
+                return 2.0 * nbytes(a[0]) + nbytes(a[2], a[8]), 0.0
+            if name == "hc_collapse":
+                return nbytes(a[6]) * (a[0].shape[0] + 1), 0.0
+            if name == "head_norm_gate":
+                return nbytes(a[0], a[6]) * 1.5, 0.0
+            if name == "softcap":
+                return 2.0 * nbytes(a[0]), 0.0
+            return nbytes(*a), 0.0
+
+        names = OLD_OPS + NEW_OPS
+        originals = {n: getattr(ops, n) for n in names}
+        depth = [0]
+
+        def wrap(name: str):
+            fn = originals[name]
+
+            def timed(*a, **k):
+                if depth[0]:
+                    return fn(*a, **k)
+                s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s_.record()
+                depth[0] += 1
+                try:
+                    r = fn(*a, **k)
+                finally:
+                    depth[0] -= 1
+                e_.record()
+                records.append((name, s_, e_, *work(name, a, k)))
+                return r
+            return timed
+
+        for n in names:
+            setattr(ops, n, wrap(n))
+        out = torch.empty(max(batch, 1), dtype=torch.int32, device=self.dev)
+        rounds = []
+        try:
+            for it in range(5):
+                records.clear()
+                entries = []
+                if prefill_tokens:
+                    req = e.cache.new_request()
+                    e.cache.append(req, prefill_tokens)
+                    entries.append(StepEntry(req, prompt))
+                for r in reqs:
+                    e.cache.append(r.cache, 1)
+                    entries.append(StepEntry(r.cache, [r.output[-1]]))
+                torch.cuda._sleep(40_000_000 if not prefill_tokens else 150_000_000)
+                ops.sample(e.runner.step(entries), out[: len(entries)])
+                torch.cuda.synchronize()
+                if prefill_tokens:
+                    e.cache.free(req)
+                if it >= 2:
+                    acc: dict = {}
+                    for name, s_, e_, by, fl in records:
+                        a = acc.setdefault(name, [0.0, 0.0, 0.0, 0.0])
+                        a[0] += s_.elapsed_time(e_)
+                        a[1] += by
+                        a[2] += 1
+                        a[3] += fl
+                    rounds.append(acc)
+        finally:
+            for n in names:
+                setattr(ops, n, originals[n])
+            ops.set_programmatic_launch(ops.DEFAULT_PDL_MASK)
+        for r in reqs:
+            e.cache.free(r.cache)
+        table = {}
+        for name in rounds[0]:
+            ms = statistics.median(r[name][0] for r in rounds)
+            _, by, calls, fl = rounds[0][name]
+            row = {"calls": int(calls), "ms": round(ms, 4), "hbm_frac": round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+            if fl:
+                row["tflops"] = round(fl / (ms * 1e-3) / 1e12, 2)
+            table[name] = row
+        return table
+
+
+def run(args) -> int:
+    import torch
+
+    pk, pk_src = peaks()
+    tokens, batch, ctx = 2048, 8, 1024
+    result = {"metric": "prefill and decode tok/s of Fegilix beside Qwen3 at equal layer sizes (6 layers, bf16, random weights)",
+              "peaks": {**{k: pk[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": pk_src},
+              "workload": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": ctx, "page_size": PAGE}, "sizes": {}}
+    for size in (args.design_sizes.split(",") if args.design_sizes else list(SIZES)):
+        s = SIZES[size]
+        entry = {}
+        for label, cfg in (("fegilix", fegilix_config(s)), ("qwen3", qwen3_config(s))):
+            b = DesignBench(cfg)
+            pre = b.prefill_ms(tokens)
+            dec, _, launches = b.device_decode(batch, ctx, max(args.warmup, 3), args.steps, check=False)
+            row = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(tokens / pre * 1e3), "decode_ms_per_step": round(dec, 4),
+                   "decode_tok_s": round(batch / dec * 1e3), "kernels_per_decode_step": launches // args.steps,
+                   "weight_mb": round(b.model.weight_bytes() / 2 ** 20, 1)}
+            if args.kernels:
+                row["prefill_by_op"] = b.op_table(0, 0, pk, prefill_tokens=tokens)
+                row["decode_by_op"] = b.op_table(batch, ctx, pk)
+            entry[label] = row
+            b.close()
+            torch.cuda.empty_cache()
+        result["sizes"][size] = entry
+    print(json.dumps(result))
+    return 0

@@ -80,6 +80,10 @@ class FegilixConfig(ModelConfig):
                     raise UnsupportedConfigError(f"{where}: mlp.kind={mlp.get('kind')!r}: only 'dense' is implemented")
                 _need(mlp, "ff", f"{where}.mlp")
 
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_positions
+
     @classmethod
     def from_dict(cls, d: Mapping[str, Any]) -> "FegilixConfig":
         name = d.get("architecture") or (d.get("architectures") or [None])[0]

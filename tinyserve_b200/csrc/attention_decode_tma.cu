@@ -511,7 +511,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     }
     const int head = kvh * G + g0 + r;
     if (a.num_splits == 1) {
-      ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(num / den);
+      ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(finish_row(num, den, mm, a.sinks, head));
     } else if constexpr (CLUSTER) {
       const int S = a.num_splits, share = (ng * D + S - 1) / S;
       if (S * share <= RECV_CAP) {
@@ -577,7 +577,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
             den += ls[sp] * c;
           }
         }
-        ((bf16*)a.out)[((size_t)qrow * a.num_heads + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(num / den);
+        ((bf16*)a.out)[((size_t)qrow * a.num_heads + kvh * G + g0 + r) * D + d] =
+            __float2bfloat16_rn(finish_row(num, den, mm, a.sinks, kvh * G + g0 + r));
       }
       return;
     }
@@ -608,7 +609,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
           den += ls[sp] * c;
         }
       }
-      ((bf16*)a.out)[((size_t)qrow * a.num_heads + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(num / den);
+      ((bf16*)a.out)[((size_t)qrow * a.num_heads + kvh * G + g0 + r) * D + d] =
+            __float2bfloat16_rn(finish_row(num, den, mm, a.sinks, kvh * G + g0 + r));
     }
     // nobody leaves while another CTA may still read its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -718,7 +720,8 @@ extern "C" int ts_decode_attention_tma(
     const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
     const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* decode_seqs,
     int num_decode, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
-    int num_splits, float* part_acc, float* part_ml, int* error_flag, cudaStream_t stream) {
+    int num_splits, float* part_acc, float* part_ml, int* error_flag, const float* sinks, cudaStream_t stream) {
+  // `sinks` (optional, [num_heads] float): a logit per head that joins the softmax's denominator without a value
   if (num_decode <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
@@ -729,6 +732,7 @@ extern "C" int ts_decode_attention_tma(
   const long long rows = num_pages_total * num_kv_heads * page_size;
   if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
   AttnArgs a;
+  a.sinks = sinks;
   a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
   a.seq_ids = decode_seqs; a.num_seqs = num_decode;

@@ -318,7 +318,8 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
     }
     if (ok && !stopped) {
       tc_fence_after();
-      const float inv = 1.f / l_sum;
+      // a head's sink logit joins the denominator: 2^(sink - m) beside the sum of the 2^(s - m)
+      const float inv = 1.f / (l_sum + (a.sinks ? exp2f(a.sinks[head] * 1.4426950408889634f - m_used) : 0.f));
       bf16* dst = (bf16*)a.out + ((size_t)(q_start + q0 + r) * a.num_heads + head) * D;
 #pragma unroll 1
       for (int c = half * (D / 32 / HS); c < (half + 1) * (D / 32 / HS); ++c) {
@@ -551,7 +552,8 @@ extern "C" int ts_prefill_attention_tcgen05(
     const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
     const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* prefill_seqs,
     int num_prefill, int max_query_len, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
-    int window, int heads_per_cta, int* error_flag, cudaStream_t stream) {
+    int window, int heads_per_cta, int* error_flag, const float* sinks, cudaStream_t stream) {
+  // `sinks` (optional, [num_heads] float): a logit per head that joins the softmax's denominator without a value
   if (num_prefill <= 0 || max_query_len <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
@@ -564,6 +566,7 @@ extern "C" int ts_prefill_attention_tcgen05(
   if (heads_per_cta != 1 && heads_per_cta != 2) return TS_ERR_BAD_ARGUMENT;
   if (heads_per_cta == 2 && group % 2 != 0) return TS_ERR_UNSUPPORTED;
   AttnArgs a;
+  a.sinks = sinks;
   a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
   a.seq_ids = prefill_seqs; a.num_seqs = num_prefill;

@@ -16,9 +16,10 @@ extern "C" int ts_paged_attention_simt(
   // `sinks` (optional, [num_heads] float): a logit per head that joins the softmax's denominator
   // without a value. `v_head_dim` (0 = head_dim): the size of a value head; when it differs from
   // head_dim the caches have different row sizes and `out` is [T, num_heads * v_head_dim].
-  if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return TS_ERR_UNSUPPORTED;
+  // The tiled kernel takes any head size up to 256; the split-K kernel sizes in steps of 16.
+  if (head_dim <= 0 || head_dim > 256) return TS_ERR_UNSUPPORTED;
   if (v_head_dim == head_dim) v_head_dim = 0;
-  if (v_head_dim < 0 || v_head_dim % 16 != 0 || v_head_dim > 256) return TS_ERR_UNSUPPORTED;
+  if (v_head_dim < 0 || v_head_dim > 256) return TS_ERR_UNSUPPORTED;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0) return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
   AttnArgs a;
@@ -37,7 +38,7 @@ extern "C" int ts_paged_attention_simt(
                                : launch_prefill<bf16>(a, max_query_len, stream);
     if (st != 0) return st;
   }
-  if (num_decode > 0 && v_head_dim != 0) {
+  if (num_decode > 0 && (v_head_dim != 0 || head_dim % 16 != 0)) {
     // the split-K kernel shares one lane layout between keys and values: single tokens take the tiled kernel
     a.seq_ids = decode_seqs; a.num_seqs = num_decode;
     return dtype == TS_DTYPE_F32 ? launch_prefill<float>(a, 1, stream) : launch_prefill<bf16>(a, 1, stream);

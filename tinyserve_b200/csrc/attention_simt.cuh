@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < DJMAX; ++j) acc[i][j] = 0.f;
-  const int dj = DV >> 4;
+  const int dj = (DV + 15) >> 4;
 
   const int qpos_first = first_pos + q0;
   const int qpos_last = first_pos + q0 + nq - 1;
@@ -82,28 +82,45 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   const int k_begin = (k_lo / PF_TK) * PF_TK;
   constexpr int VEC = Vec<T>::N;
   const int chunks = D / VEC, vchunks = DV / VEC;
+  const bool vec_ok = (D % VEC == 0) && (DV % VEC == 0);
 
   for (int k0 = k_begin; k0 <= qpos_last; k0 += PF_TK) {
     __syncthreads();   // previous tile fully consumed (and Qs/row state initialised)
     // ---- stage keys and values k0 .. k0+TK-1 (zeros outside the request's visible range)
-    for (int idx = tid; idx < PF_TK * (chunks + vchunks); idx += PF_THREADS) {
-      const int kk = idx / (chunks + vchunks), c = idx - kk * (chunks + vchunks);
-      const bool is_key = c < chunks;
-      const int cc = is_key ? c : c - chunks;
-      const int kpos = k0 + kk;
-      float f[VEC];
-      if (kpos >= k_lo && kpos <= qpos_last) {
-        const size_t row = kv_row_of(table, kpos, kvh, a);
-        Vec<T> raw;
-        raw.load(is_key ? kc + row * D + (size_t)cc * VEC : vc + row * DV + (size_t)cc * VEC);
-        raw.unpack(f);
-      } else {
+    if (vec_ok) {
+      for (int idx = tid; idx < PF_TK * (chunks + vchunks); idx += PF_THREADS) {
+        const int kk = idx / (chunks + vchunks), c = idx - kk * (chunks + vchunks);
+        const bool is_key = c < chunks;
+        const int cc = is_key ? c : c - chunks;
+        const int kpos = k0 + kk;
+        float f[VEC];
+        if (kpos >= k_lo && kpos <= qpos_last) {
+          const size_t row = kv_row_of(table, kpos, kvh, a);
+          Vec<T> raw;
+          raw.load(is_key ? kc + row * D + (size_t)cc * VEC : vc + row * DV + (size_t)cc * VEC);
+          raw.unpack(f);
+        } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) f[e] = 0.f;
+          for (int e = 0; e < VEC; ++e) f[e] = 0.f;
+        }
+        float* dst = is_key ? Ks + kk * DS + cc * VEC : Vs + kk * DV + cc * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dst[e] = f[e];
       }
-      float* dst = is_key ? Ks + kk * DS + cc * VEC : Vs + kk * DV + cc * VEC;
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) dst[e] = f[e];
+    } else {
+      // head sizes that are no multiple of a 16-byte vector: element by element
+      for (int idx = tid; idx < PF_TK * (D + DV); idx += PF_THREADS) {
+        const int kk = idx / (D + DV), c = idx - kk * (D + DV);
+        const bool is_key = c < D;
+        const int cc = is_key ? c : c - D;
+        const int kpos = k0 + kk;
+        float f = 0.f;
+        if (kpos >= k_lo && kpos <= qpos_last) {
+          const size_t row = kv_row_of(table, kpos, kvh, a);
+          f = is_key ? to_float(kc[row * D + cc]) : to_float(vc[row * DV + cc]);
+        }
+        if (is_key) Ks[kk * DS + cc] = f; else Vs[kk * DV + cc] = f;
+      }
     }
     __syncthreads();
     // ---- scores: thread (ty, tx) owns rows ty*4..+3, keys tx*2..+1
@@ -176,7 +193,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
       for (int i = 0; i < 4; ++i) p[i] = Ss[(ty * 4 + i) * (PF_TK + 1) + kk];
 #pragma unroll
       for (int j = 0; j < DJMAX; ++j) {
-        if (j < dj) {
+        if (j < dj && tx + 16 * j < DV) {
           const float vv = Vs[kk * DV + tx + 16 * j];
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i][j] = fmaf(p[i], vv, acc[i][j]);
@@ -192,7 +209,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
     if (r < nq) {
 #pragma unroll
       for (int j = 0; j < DJMAX; ++j)
-        if (j < dj)
+        if (j < dj && tx + 16 * j < DV)
           out[((size_t)(row0 + q0 + r) * a.num_heads + head) * DV + tx + 16 * j] =
               from_float<T>(finish_row(acc[i][j], row_l[r], row_m[r], a.sinks, head));
     }
@@ -432,7 +449,7 @@ static int launch_prefill_dj(const AttnArgs& a, int max_query_len, cudaStream_t 
 
 template <typename T>
 static int launch_prefill(const AttnArgs& a, int max_query_len, cudaStream_t stream) {
-  const int dj = (a.v_head_dim ? a.v_head_dim : a.head_dim) / 16;
+  const int dj = ((a.v_head_dim ? a.v_head_dim : a.head_dim) + 15) / 16;
   if (dj <= 2) return launch_prefill_dj<T, 2>(a, max_query_len, stream);
   if (dj <= 4) return launch_prefill_dj<T, 4>(a, max_query_len, stream);
   if (dj <= 8) return launch_prefill_dj<T, 8>(a, max_query_len, stream);

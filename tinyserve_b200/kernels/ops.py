@@ -50,14 +50,14 @@ _SIGNATURES: dict[str, list[Any]] = {
                                 _vp, _vp],
     "ts_decode_attention_mma_slots": [_i],
     "ts_decode_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-                                _i, _vp, _vp, _vp, _vp],
+                                _i, _vp, _vp, _vp, _vp, _vp],
     "ts_decode_attention_tma_fused": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp,
                                       _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp],
     "ts_decode_attention_tma_slots": [_i],
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
     "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                     _f, _i, _i, _vp, _vp],
+                                     _f, _i, _i, _vp, _vp, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream_parts": [_i, _i, _i],
@@ -385,20 +385,23 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError("paged_attention: cache layout must be [pages, kv_heads, page_size, head_dim]")
     if out.numel() != t * hq * dv or hq % hkv:
         raise KernelError("paged_attention: out shape or head grouping")
-    if d % 16 or d > 256 or dv % 16 or dv > 256:
-        raise KernelError(f"paged_attention: head sizes {d}/{dv} must be multiples of 16 up to 256")
+    tma_ok = (dt == torch.bfloat16 and d in (64, 128) and dv == d and (page_size == 8 or page_size % 16 == 0)
+              and k_cache.shape[0] * hkv * page_size < 2 ** 31)
+    # sink logits are known to the tcgen05 prompt kernel, the TMA decode kernel and the CUDA-core
+    # kernels; a value head size of its own and odd head sizes to the CUDA-core kernels only
+    simt_only = dv != d or d % 16 != 0 or (sinks is not None and not (tma_ok and PREFILL_ATTENTION == "tcgen05"))
+    if d > 256 or dv > 256:
+        raise KernelError(f"paged_attention: head sizes {d}/{dv} must be at most 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("paged_attention: block_tables must be [requests, width]")
     if sinks is not None and (sinks.shape != (hq,) or sinks.dtype != torch.float32):
         raise KernelError("paged_attention: sinks must be float32, one per query head")
     _check_indices("paged_attention", block_tables, ctx, page_size, k_cache.shape[0])
     num_prefill = ctx.num_prefill
-    if sinks is not None or dv != d:
-        # the CUDA-core kernels know sink logits and a value head size of its own
+    if simt_only:
+        # the CUDA-core kernels know sink logits, a value head size of its own and odd head sizes
         _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, sinks, num_prefill)
         return
-    tma_ok = (dt == torch.bfloat16 and d in (64, 128) and (page_size == 8 or page_size % 16 == 0)
-              and k_cache.shape[0] * hkv * page_size < 2 ** 31)
     if num_prefill and dt == torch.bfloat16 and d <= 128:
         # prefill rows on the tensor cores; the decode rows follow below
         if tma_ok and PREFILL_ATTENTION == "tcgen05":
@@ -411,7 +414,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                 _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
                 hq, hkv, d, page_size, float(scale), int(window),
                 _prefill_heads_per_cta(ctx, hq, hkv),
-                _error_word(q.device).data_ptr(), _stream()), "prefill_attention_tcgen05")
+                _error_word(q.device).data_ptr(), _opt(sinks, "sinks", torch.float32), _stream()),
+                "prefill_attention_tcgen05")
         elif tma_ok:
             _check(_fn("ts_prefill_attention_tma")(
                 _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), k_cache.shape[0],
@@ -452,7 +456,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             # tiles fetched by the TMA unit (tensor copies, 128-byte swizzle)
             _check(_fn("ts_decode_attention_tma")(
                 _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
-                k_cache.shape[0], *common), "decode_attention_tma")
+                k_cache.shape[0], *common[:-1], _opt(sinks, "sinks", torch.float32), common[-1]), "decode_attention_tma")
         else:
             # tiles fetched row by row with bulk copies
             _check(_fn("ts_decode_attention_mma")(
@@ -468,7 +472,7 @@ def _paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     t, hq, d = q.shape
     hkv, dv, dt = k_cache.shape[1], v_cache.shape[3], q.dtype
     splits, part_acc, part_ml = 1, None, None
-    if ctx.num_decode and dv == d:
+    if ctx.num_decode and dv == d and d % 16 == 0:
         splits = decode_splits(ctx.num_decode, hkv, hq // hkv, ctx.max_context_len)
         if splits > 1:
             part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)

@@ -152,8 +152,8 @@ class GatedSinkAttention(Mixer):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         for what, size in (("key_dim", key_dim), ("value_dim", value_dim)):
-            if size <= 0 or size % 16 or size > 256:
-                raise ValueError(f"{what}={size}: the attention kernels take head sizes in steps of 16 up to 256")
+            if not 0 < size <= 256:
+                raise ValueError(f"{what}={size}: the attention kernels take head sizes up to 256")
         self.prefix, self.h = prefix, int(hidden_size)
         self.heads, self.groups, self.d, self.dv = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
         self.scale, self.qk_norm, self.eps = float(scale), bool(qk_norm), float(qk_norm_eps)
