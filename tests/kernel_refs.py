@@ -171,6 +171,14 @@ def act_mul(gate_up, out, activation) -> None:
     out.copy_((a * u).to(out.dtype))
 
 
+def gemm_gated(x, w_gate_up, out, arena, activation) -> None:
+    if activation == "silu":
+        gemm_swiglu(x, w_gate_up, out, arena)
+        return
+    gu = (x.float() @ w_gate_up.float().t())
+    act_mul(gu, out, activation)
+
+
 def softcap(logits, cap) -> None:
     logits.copy_(cap * torch.tanh(logits / cap))
 
@@ -342,7 +350,7 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, st
 
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
           "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
-          "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare"]
+          "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated"]
 
 
 @contextmanager

@@ -97,6 +97,25 @@ def test_gate_kernels(dtype) -> None:
         torch.testing.assert_close(a.float(), b.float(), **_tol(dtype))
 
 
+@pytest.mark.parametrize("m, inter, k", [(3, 96, 64), (8, 3072, 1024), (16, 1024, 512), (40, 200, 72), (300, 3072, 1024), (2048, 3072, 1024)])
+def test_gated_product_with_gelu(m, inter, k) -> None:
+    """The three routes of the gate/up product with the tanh form of GELU (skinny, tcgen05 epilogue,
+    product + activation kernel), chosen by the shape, against the reference."""
+    from tinyserve_b200.kernels import ops
+
+    x, w = _rand(m, k, seed=1, dtype=torch.bfloat16), _rand(2 * inter, k, seed=2, scale=k ** -0.5, dtype=torch.bfloat16)
+    got, want = torch.empty(m, inter, dtype=torch.bfloat16, device="cuda"), torch.empty(m, inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_gated(x, w, got, Arena(), "gelu_tanh")
+    ops.check_device_errors()
+    refs.gemm_gated(x, w, want, None, "gelu_tanh")
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    x32, w32 = x.float(), w.float()
+    got32, want32 = torch.empty(m, inter, device="cuda"), torch.empty(m, inter, device="cuda")
+    ops.gemm_gated(x32, w32, got32, Arena(), "gelu_tanh")
+    refs.gemm_gated(x32, w32, want32, None, "gelu_tanh")
+    torch.testing.assert_close(got32, want32, atol=2e-5, rtol=2e-4)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("taps, channels", [(1, 40), (2, 96), (4, 384), (8, 33)])
 def test_causal_conv_carries_its_state(dtype, taps, channels) -> None:

@@ -40,6 +40,14 @@
 
 namespace ts {
 
+// FUSE as a template argument: 0 = a plain product, 1 = silu(gate) * up with the rounding points of the
+// separate kernels, FUSE_GELU_TANH = gelu_tanh(gate) * up in 32-bit, rounded once.
+constexpr int FUSE_GELU_TANH = 2;
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+}
+
+
 constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_KSTEP = SK_WARPS * 32;    // distance between a warp's k blocks
@@ -116,7 +124,7 @@ __device__ __forceinline__ uint4 normed_fragment(const uint4& rv, const uint4& w
 // The forms of up to 16 rows are held to 128 registers so that two CTAs of 8 warps fit an SM: the
 // fused gate/up product of 9 to 16 rows took 146 and ran its 192 CTAs in two rounds (10.4 us in a
 // recorded decode step of 16 rows, against 6.6 us for the 8-row form).
-template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false,
+template <typename TOut, int NT, int RT, int FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false,
           int WARPS = SK_WARPS>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && NT <= 2) ? 2 : 1)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
@@ -319,9 +327,13 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
       if (ksplit > 1) {
       } else if constexpr (FUSE) {
         // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
-        const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
-        const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
-        out[(size_t)m * N + n0 + row] = from_float<TOut>(sv * uv);
+        if constexpr (FUSE == FUSE_GELU_TANH) {
+          out[(size_t)m * N + n0 + row] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
+        } else {
+          const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
+          const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
+          out[(size_t)m * N + n0 + row] = from_float<TOut>(sv * uv);
+        }
       } else if constexpr (!RESID) {
         out[(size_t)m * N + n0 + row] = from_float<TOut>(s);
       }
@@ -365,7 +377,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
   }
 }
 
-template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool NORMX = false, bool RESID = false>
+template <typename TOut, int NT, int RT, int FUSE, int SK_PF, bool NORMX = false, bool RESID = false>
 static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream,
                          const SkinnyNorm& nrm = SkinnyNorm()) {
   constexpr int TILES = FUSE ? 2 * RT : RT;
@@ -581,7 +593,7 @@ static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, 
 // (K <= PF * WARPS * 32). FUSE, NORMX, RESID as in gemm_skinny_kernel; RESID leaves the sums of
 // squares per 8 columns (N / 8 parts a row).
 // XR = 1: up to 8 rows of x; XR = 2: up to 16 (the tile's rows g + 8 are then x rows too).
-template <typename TOut, bool FUSE, bool NORMX, bool RESID, int WARPS, int PF, int XR>
+template <typename TOut, int FUSE, bool NORMX, bool RESID, int WARPS, int PF, int XR>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                    TOut* __restrict__ out, int M, int N, int K,
                                                                    SkinnyNorm nrm) {
@@ -703,9 +715,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
   } else if (om < M) {
     if constexpr (FUSE) {
       // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
-      const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
-      const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
-      out[(size_t)om * N + n0 + orow] = from_float<TOut>(sv * uv);
+      if constexpr (FUSE == FUSE_GELU_TANH) {
+        out[(size_t)om * N + n0 + orow] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
+      } else {
+        const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
+        const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
+        out[(size_t)om * N + n0 + orow] = from_float<TOut>(sv * uv);
+      }
     } else {
       out[(size_t)om * N + n0 + orow] = from_float<TOut>(s);
     }
@@ -727,7 +743,7 @@ static bool to_stream_takes_h8(int M, int N, int K) {
 }
 static bool normed_takes_h8(int M, int N, int K) { return M <= 16 && h8_spreads_better(N) && K <= SK_H8_PF * SK_H8_WARPS * 32; }
 // The plain and the SwiGLU product of up to 16 rows: narrow outputs take the tall CTAs, wide ones CTAs of 8 warps.
-template <typename TOut, bool FUSE>
+template <typename TOut, int FUSE>
 static int launch_h8_plain(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   const SkinnyNorm nrm = SkinnyNorm();
   if (K <= SK_H8_PF * SK_H8_WARPS * 32) {
@@ -761,9 +777,9 @@ static int dispatch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N
   return dispatch_skinny_nt<TOut, 8>(x, w, out, M, N, K, stream);
 }
 
-template <int NT>
+template <int NT, int FUSE = 1>
 static int dispatch_swiglu_nt(const bf16* x, const bf16* w, bf16* out, int M, int inter, int K, cudaStream_t stream) {
-  return launch_skinny<bf16, NT, 1, true, 4>(x, w, out, M, inter, K, stream);
+  return launch_skinny<bf16, NT, 1, FUSE, 4>(x, w, out, M, inter, K, stream);
 }
 
 }  // namespace ts
@@ -797,6 +813,23 @@ extern "C" int ts_gemm_skinny_swiglu(const void* x, const void* w, void* out, in
   if (M <= 8) return dispatch_swiglu_nt<1>(xp, wp, op, M, inter, K, stream);
   if (M <= 16) return dispatch_swiglu_nt<2>(xp, wp, op, M, inter, K, stream);
   return dispatch_swiglu_nt<4>(xp, wp, op, M, inter, K, stream);
+}
+
+// The same with a choice of activation: 0 = silu (as above), 1 = the tanh form of GELU.
+extern "C" int ts_gemm_skinny_gated(const void* x, const void* w, void* out, int M, int inter, int K, int activation,
+                                    cudaStream_t stream) {
+  if (activation == 0) return ts_gemm_skinny_swiglu(x, w, out, M, inter, K, stream);
+  if (activation != 1) return TS_ERR_BAD_ARGUMENT;
+  if (M <= 0 || inter <= 0) return 0;
+  if (M > 32 || K <= 0 || K % 32 != 0 || inter % 16 != 0) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)w;
+  bf16* op = (bf16*)out;
+  if (plain_takes_h8(M, inter, K)) return launch_h8_plain<bf16, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
+  if (M <= 8) return dispatch_swiglu_nt<1, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
+  if (M <= 16) return dispatch_swiglu_nt<2, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
+  return dispatch_swiglu_nt<4, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
 }
 
 // out = rms_norm(resid) * w^T where the norm is made on the fly (NORMX above): resid16 [M, K] bf16,

@@ -35,7 +35,11 @@ constexpr int TG_THREADS = 192;     // TMA warp, MMA warp, four epilogue warps
 
 // One warp's share of an accumulator tile (its 32 tensor-memory lanes = 32 rows, BN columns from
 // tmem_acc) -> out: cast and store, or silu(gate) * up of the two halves (SWIGLU).
-template <int BN, typename TOut, bool SWIGLU>
+// SWIGLU as a template argument: 0 = a plain product, GATED_SILU = silu(gate) * up with the rounding points
+// of the separate kernels, GATED_GELU_TANH = gelu_tanh(gate) * up in 32-bit.
+constexpr int GATED_SILU = 1, GATED_GELU_TANH = 2;
+
+template <int BN, typename TOut, int SWIGLU>
 __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, int N, int n0, TOut* __restrict__ out) {
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
   if constexpr (SWIGLU) {
@@ -51,8 +55,17 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float gv = round_to<bf16>(__uint_as_float(g[j])), uv = round_to<bf16>(__uint_as_float(u[j]));
-          f[j] = round_to<bf16>(__fdividef(gv, 1.f + __expf(-gv))) * uv;
+          if constexpr (SWIGLU == GATED_GELU_TANH) {
+            // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) * up in 32-bit, rounded once; the tanh is the
+            // hardware approximation, whose error lies below the rounding of the result
+            const float z = __uint_as_float(g[j]);
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+            f[j] = 0.5f * z * (1.f + th) * __uint_as_float(u[j]);
+          } else {
+            const float gv = round_to<bf16>(__uint_as_float(g[j])), uv = round_to<bf16>(__uint_as_float(u[j]));
+            f[j] = round_to<bf16>(__fdividef(gv, 1.f + __expf(-gv))) * uv;
+          }
         }
         if (n0 + c * 32 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -104,7 +117,7 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
 // rows fastest, so CTAs that run together share weight tiles in L2). The accumulator is double-
 // buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i, the
 // MMA warp already accumulates tile i + 1.
-template <int BN, int STAGES, typename TOut, bool SWIGLU = false>
+template <int BN, int STAGES, typename TOut, int SWIGLU = false>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   TOut* __restrict__ out, int M, int N, int K,
@@ -245,7 +258,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
 // its commits arrive at the barriers of both CTAs; both CTAs' TMA copies report their bytes to the
 // even CTA's "full" barrier; each CTA's epilogue warps drain their own tensor memory and hand the
 // accumulator back to the even CTA's MMA thread.
-template <int STAGES, typename TOut, bool SWIGLU>
+template <int STAGES, typename TOut, int SWIGLU>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                        const __grid_constant__ CUtensorMap map_w,
                                                                        TOut* __restrict__ out, int M, int N, int K,
@@ -404,7 +417,7 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, typename TOut, bool SWIGLU = false>
+template <int BN, int STAGES, typename TOut, int SWIGLU = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
                      cudaStream_t stream) {
   const size_t smem = (size_t)STAGES * (TG_BM + BN) * TG_BK * 2 + 1024;
@@ -417,7 +430,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, in
   return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag);
 }
 
-template <int STAGES, typename TOut, bool SWIGLU>
+template <int STAGES, typename TOut, int SWIGLU>
 static int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
                           cudaStream_t stream) {
   const size_t smem = (size_t)STAGES * (TG_BM + 128) * TG_BK * 2 + 1024;
@@ -469,6 +482,20 @@ extern "C" int ts_gemm_tcgen05_swiglu(const void* x, const void* w, void* out, i
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, 2 * inter, K, 128)) return TS_ERR_UNSUPPORTED;
-  if (pair) return launch_tc_pair<6, bf16, true>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
-  return launch_tc<256, 4, bf16, true>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+  if (pair) return launch_tc_pair<6, bf16, GATED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+  return launch_tc<256, 4, bf16, GATED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+}
+
+// The same with a choice of activation: 0 = silu (as above), 1 = the tanh form of GELU.
+extern "C" int ts_gemm_tcgen05_gated(const void* x, const void* w, void* out, int M, int inter, int K, int pair,
+                                     int activation, int* error_flag, cudaStream_t stream) {
+  if (activation == 0) return ts_gemm_tcgen05_swiglu(x, w, out, M, inter, K, pair, error_flag, stream);
+  if (activation != 1) return TS_ERR_BAD_ARGUMENT;
+  if (M <= 0 || inter <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, 2 * inter, K, 128)) return TS_ERR_UNSUPPORTED;
+  if (pair) return launch_tc_pair<6, bf16, GATED_GELU_TANH>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+  return launch_tc<256, 4, bf16, GATED_GELU_TANH>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
 }

@@ -87,6 +87,111 @@ __global__ void hc_mix_norm_kernel(float* __restrict__ lanes, const float* __res
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(us[i] * rstd * to_float(norm_w[i]));
 }
 
+// The same for a lane count known at compile time and rows of a multiple of four 16-byte-aligned
+// values: the connection weights sit in registers and every access is 16 bytes wide (8 for bf16).
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+template <> struct Quad<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* f) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float* f) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&a);
+    v.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = v;
+  }
+};
+
+template <typename T, int S>
+__global__ void hc_mix_norm_vec_kernel(float* __restrict__ lanes, const float* __restrict__ fresh,
+                                       const T* __restrict__ delta, const float* __restrict__ mix_prev,
+                                       const float* __restrict__ out_prev, const float* __restrict__ in_next,
+                                       const T* __restrict__ norm_w, T* __restrict__ out, int num_tokens, int hidden,
+                                       float eps) {
+  extern __shared__ __align__(16) float us[];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  float mix[S][S], wo[S], wi[S];
+#pragma unroll
+  for (int a = 0; a < S; ++a) {
+    wi[a] = in_next[a];
+    wo[a] = delta ? out_prev[a] : 0.f;
+#pragma unroll
+    for (int b = 0; b < S; ++b) mix[a][b] = delta ? mix_prev[a * S + b] : (a == b ? 1.f : 0.f);
+  }
+  const int row = blockIdx.x;
+  const size_t lane_stride = (size_t)num_tokens * hidden;
+  float* x = lanes + (size_t)row * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float nx[S][4];
+    if (fresh) {
+      float v[4];
+      Quad<float>::load(fresh + (size_t)row * hidden + i, v);
+#pragma unroll
+      for (int t = 0; t < S; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) nx[t][e] = v[e];
+    } else {
+      float ox[S][4];
+#pragma unroll
+      for (int a = 0; a < S; ++a) Quad<float>::load(x + a * lane_stride + i, ox[a]);
+      if (delta) {
+        float y[4];
+        Quad<T>::load(delta + (size_t)row * hidden + i, y);
+#pragma unroll
+        for (int t = 0; t < S; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float acc = 0.f;
+#pragma unroll
+            for (int a = 0; a < S; ++a) acc = fmaf(mix[a][t], ox[a][e], acc);
+            nx[t][e] = fmaf(wo[t], y[e], acc);
+          }
+      } else {
+#pragma unroll
+        for (int t = 0; t < S; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) nx[t][e] = ox[t][e];
+      }
+    }
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int t = 0; t < S; ++t) {
+      if (fresh || delta) Quad<float>::store(x + t * lane_stride + i, nx[t]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) u[e] = fmaf(wi[t], nx[t][e], u[e]);
+    }
+    Quad<float>::store(us + i, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss = fmaf(u[e], u[e], ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)row * hidden;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float u[4], w[4];
+    Quad<float>::load(us + i, u);
+    Quad<T>::load(norm_w + i, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) u[e] = u[e] * rstd * w[e];
+    Quad<T>::store(o + i, u);
+  }
+}
+
 // sum_out[r] = sum_t (sum_s mix[s][t] x_s + out[t] y) at row rows[r] (or r); lanes stay as they are.
 template <typename T>
 __global__ void hc_collapse_kernel(const float* __restrict__ lanes, const float* __restrict__ fresh,
@@ -134,6 +239,22 @@ extern "C" int ts_hc_mix_norm(float* lanes, const float* fresh, const void* delt
   if (hidden > 48 * 1024 / 4) return TS_ERR_UNSUPPORTED;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t smem = sizeof(float) * hidden;
+  const bool aligned = ((((uintptr_t)lanes) | ((uintptr_t)fresh) | ((uintptr_t)delta) | ((uintptr_t)norm_w) | ((uintptr_t)out)) & 15) == 0;
+  if (aligned && hidden % 4 == 0 && num_lanes <= 4 && (dtype == TS_DTYPE_F32 || dtype == TS_DTYPE_BF16)) {
+    const int vthreads = hidden >= 2048 ? 256 : 128;
+#define TS_HC_CASE(T_, S_)                                                                                              \
+  return launch(hc_mix_norm_vec_kernel<T_, S_>, num_tokens, vthreads, smem, stream, lanes, fresh, (const T_*)delta,      \
+                mix_prev, out_prev, in_next, (const T_*)norm_w, (T_*)out, num_tokens, hidden, eps)
+#define TS_HC_LANES(T_)                       \
+  if (num_lanes == 1) { TS_HC_CASE(T_, 1); }  \
+  if (num_lanes == 2) { TS_HC_CASE(T_, 2); }  \
+  if (num_lanes == 3) { TS_HC_CASE(T_, 3); }  \
+  TS_HC_CASE(T_, 4)
+    if (dtype == TS_DTYPE_F32) { TS_HC_LANES(float); }
+    TS_HC_LANES(bf16);
+#undef TS_HC_LANES
+#undef TS_HC_CASE
+  }
   if (dtype == TS_DTYPE_F32)
     return launch(hc_mix_norm_kernel<float>, num_tokens, threads, smem, stream, lanes, fresh, (const float*)delta,
                   mix_prev, out_prev, in_next, (const float*)norm_w, (float*)out, num_lanes, num_tokens, hidden, eps);

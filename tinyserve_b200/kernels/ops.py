@@ -68,6 +68,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ts_gemm_tcgen05_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -753,6 +755,38 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
     silu_mul(gate_up, out)
+
+
+def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any, activation: str) -> None:
+    """``out[M, I] = act(x Wgate^T) * (x Wup^T)`` with a choice of activation (``ACTIVATIONS``). "silu"
+    is :func:`gemm_swiglu`. "gelu_tanh" takes the same three routes: a few bf16 rows the skinny product
+    with the activation in the same pass, many bf16 rows of a wide matrix the tcgen05 product with the
+    activation in its epilogue, anything else a product into scratch and the activation kernel. The
+    activation and the product of the halves are 32-bit, rounded once."""
+    if activation == "silu":
+        gemm_swiglu(x, w_gate_up, out, arena)
+        return
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_gated: unknown activation {activation!r}")
+    m, k = x.shape
+    inter = out.shape[1]
+    if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
+        raise KernelError("gemm_gated: shape or dtype mismatch")
+    code = ACTIVATIONS[activation]
+    if (x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0
+            and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
+        _check(_fn("ts_gemm_skinny_gated")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
+                                           code, _stream()), "gemm_gated")
+        return
+    tiles = tcgen05_tiles(m, inter, 128)
+    if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0 and tiles:
+        _check(_fn("ts_gemm_tcgen05_gated")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
+                                            int(tiles == "pairs"), code, _error_word(x.device).data_ptr(), _stream()),
+               "gemm_tcgen05_gated")
+        return
+    gate_up = arena.take((m, 2 * inter), x.dtype)
+    gemm(x, w_gate_up, gate_up)
+    act_mul(gate_up, out, activation)
 
 
 # Steps of a few rows (decode) fold the RMSNorm into the products around it: the product that

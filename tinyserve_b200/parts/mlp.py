@@ -57,8 +57,8 @@ class GatedMLP(FeedForward):
     """``y = (act(x Wgate^T) * (x Wup^T)) Wdown^T`` with a choice of activation ("silu",
     "gelu_tanh": ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``) and of tensor names
     (``names``: role "gate" / "up" / "down" -> name after the prefix). Gate and up come from one
-    product with the merged matrix; the activation and the product of the halves are 32-bit and
-    rounded once."""
+    product with the merged matrix, with the activation in the same kernel where the framework
+    has one for the step's shape (``ops.gemm_gated``)."""
 
     recordable = EVERY_STEP
 
@@ -87,10 +87,8 @@ class GatedMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         t = x.shape[0]
-        both = ctx.arena.take((t, 2 * self.intermediate_size), ctx.dtype)
-        ops.gemm(x, self.w_gate_up, both)
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        ops.act_mul(both, act, self.activation)
+        ops.gemm_gated(x, self.w_gate_up, act, ctx.arena, self.activation)
         out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
         ops.gemm(act, self.w_down, out)
         return out
