@@ -137,7 +137,7 @@ def delta_rule_scan(q, k, v, beta, decay):
 
 
 def mlstm_scan(q, k, v, log_i, log_f):
-    """Matrix memory with a running maximum that starts at 0. q, k ``[T, H, D]`` (q already
+    """Matrix memory with the stabiliser m (a running maximum) initialised to 0. q, k ``[T, H, D]`` (q already
     scaled), v ``[T, H, Dv]``, log gates ``[T, H]``."""
     t, heads, d = q.shape
     dv = v.shape[-1]

@@ -10,27 +10,30 @@
 
 namespace ts {
 
+constexpr int QP_WARPS = 4;          // warps (heads in flight) per CTA
+constexpr int QP_MAX_DIM = 256;      // largest head the staging rows hold
+
+// One head by one warp: the head is read once from global memory into the warp's row of shared
+// memory (as 32-bit values), the sum of squares is formed on the way, and every element is then
+// written with its rotation partner taken from that row.
 template <typename T>
 __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const T* __restrict__ w, float eps,
                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                                 int rotary_dim, int d, T* __restrict__ dst, int lane) {
-  float rstd = 1.f;
-  if (w) {
-    float ss = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float v = to_float(x[i]);
-      ss = fmaf(v, v, ss);
-    }
-    rstd = rsqrtf(warp_sum(ss) / (float)d + eps);
+                                                 int rotary_dim, int d, T* __restrict__ dst, int lane,
+                                                 float* __restrict__ row) {
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float v = to_float(x[i]);
+    row[i] = w ? v * to_float(w[i]) : v;
+    ss = fmaf(v, v, ss);
   }
+  const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+  __syncwarp();
   const int half = rotary_dim >> 1;
   for (int i = lane; i < d; i += 32) {
-    float y = to_float(x[i]) * rstd;
-    if (w) y *= to_float(w[i]);
+    float y = row[i] * rstd;
     if (i < rotary_dim) {
-      const int p = i < half ? i + half : i - half;
-      float yp = to_float(x[p]) * rstd;
-      if (w) yp *= to_float(w[p]);
+      const float yp = row[i < half ? i + half : i - half] * rstd;
       const int f = i < half ? i : i - half;
       const float c = cos_t[f], s = sin_t[f];
       y = i < half ? y * c - yp * s : y * c + yp * s;
@@ -46,6 +49,8 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
                                    const float* __restrict__ sin_tab, int rotary_dim, const int* __restrict__ slots,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens,
                                    int heads, int kv_heads, int d, int dv, T* __restrict__ q_out) {
+  __shared__ float rows[QP_WARPS][QP_MAX_DIM];
+  float* row = rows[threadIdx.x >> 5];
   pdl_trigger();
   pdl_wait();
   const int jobs = heads + (k_in ? 2 * kv_heads : 0);
@@ -57,7 +62,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   if (job < heads) {
     norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_w, eps, cos_t, sin_t, rotary_dim, d,
-                     q_out + ((size_t)t * heads + job) * d, lane);
+                     q_out + ((size_t)t * heads + job) * d, lane, row);
     return;
   }
   const int slot = slots[t];
@@ -65,7 +70,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   if (job < heads + kv_heads) {
     const int g = job - heads;
     norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_w, eps, cos_t, sin_t, rotary_dim, d,
-                     k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane);
+                     k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane, row);
     return;
   }
   const int g = job - heads - kv_heads;
@@ -84,10 +89,11 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
                               int page_size, int num_tokens, int heads, int kv_heads, int d, int dv, void* q_out,
                               int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  if (d > QP_MAX_DIM) return TS_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && (!cos_tab || !sin_tab))) return TS_ERR_BAD_ARGUMENT;
   if (k_in && (!v_in || !slots || !k_cache || !v_cache || page_size <= 0)) return TS_ERR_BAD_ARGUMENT;
   const long long warps = (long long)num_tokens * (heads + (k_in ? 2 * kv_heads : 0));
-  const int threads = 128;
+  const int threads = QP_WARPS * 32;
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
   if (dtype == TS_DTYPE_F32)
     return launch(qkv_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)q_in, q_stride, (const float*)k_in,

@@ -133,7 +133,7 @@ class GatedSinkAttention(Mixer):
     ``v = W_v h`` (``num_kv_heads x value_dim``: values may have a head size of their own), no
     biases; optional RMSNorm of q and k per head (plain weights shared by the heads) before the
     rotation that the layer's position encoding asks for; scores ``scale * q . k``, causal; the
-    softmax's denominator also holds ``exp(sink_h)``, which has no key and no value; the
+    softmax's denominator gets one more term per head, ``exp(sink_h)``, to which no value belongs; the
     concatenated heads are multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``. With
     ``own_kv=False`` the layer has no key/value tensors and only ever runs as a call that reads
     another call's cache. ``names`` maps the roles "q", "k", "v", "gate", "out", "q_norm",

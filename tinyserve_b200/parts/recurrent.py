@@ -2,7 +2,7 @@
 
 ``MLSTMMixer``: the matrix memory of xLSTM. Per head, with log gates
 ``i = cap tanh((W_i h + b_i) / cap)`` and ``f = logsigmoid(cap tanh((W_f h + b_f) / cap))`` and a
-running maximum ``m`` that starts at 0: ``m' = max(f + m, i)``;
+stabiliser ``m`` (a running maximum, 0 for a fresh state): ``m' = max(f + m, i)``;
 ``S <- e^(f + m - m') S + e^(i - m') k v^T``; ``n`` likewise with ``k``;
 ``o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)`` with ``q`` scaled by ``dim^-1/2``. Each head's ``o``
 is divided by its root mean square, the heads are concatenated, multiplied by a weight and by
