@@ -127,8 +127,10 @@ class DesignBench(Bench):
                 pairs = sum(n * (c - n) + n * (n + 1) / 2 for n, c in zip(ctx.query_lens, ctx.context_lens))
                 return (float(sum(ctx.context_lens)) * kc.shape[1] * (kc.shape[3] + vc.shape[3]) * kc.element_size(),
                         2.0 * heads * (kc.shape[3] + vc.shape[3]) * pairs)
-            if name in ("qk_norm_rope_write", "qkv_prepare"):
+            if name == "qk_norm_rope_write":
                 return 2.0 * nbytes(a[0]), 0.0
+            if name == "qkv_prepare":         # q, k and v rows read and written
+                return 2.0 * nbytes(a[0], a[1], a[2]), 0.0
             if name == "embed":
                 return nbytes(a[0], a[2]) + a[0].numel() * a[1].shape[1] * a[1].element_size(), 0.0
             if name == "mlstm_scan":          # state in and out, the rows read, the read-out written; 6 flops per state element and token

@@ -13,24 +13,58 @@ namespace ts {
 constexpr int QP_WARPS = 4;          // warps (heads in flight) per CTA
 constexpr int QP_MAX_DIM = 256;      // largest head the staging rows hold
 
+// Two neighbouring elements in one access.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ void load(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+  static constexpr uintptr_t MASK = 7;
+};
+template <> struct Pair<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float& a, float& b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+    a = __uint_as_float(v << 16); b = __uint_as_float(v & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+  static constexpr uintptr_t MASK = 3;
+};
+
 // One head by one warp: the head is read once from global memory into the warp's row of shared
 // memory (as 32-bit values), the sum of squares is formed on the way, and every element is then
-// written with its rotation partner taken from that row.
+// written with its rotation partner taken from that row. Heads of an even size at an aligned
+// address move two elements per access.
 template <typename T>
 __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const T* __restrict__ w, float eps,
                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                  int rotary_dim, int d, T* __restrict__ dst, int lane,
                                                  float* __restrict__ row) {
+  const bool pairs = (d & 1) == 0 && ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w)) & Pair<T>::MASK) == 0;
   float ss = 0.f;
-  for (int i = lane; i < d; i += 32) {
-    const float v = to_float(x[i]);
-    row[i] = w ? v * to_float(w[i]) : v;
-    ss = fmaf(v, v, ss);
+  if (pairs) {
+    for (int i = 2 * lane; i < d; i += 64) {
+      float a, b, wa = 1.f, wb = 1.f;
+      Pair<T>::load(x + i, a, b);
+      if (w) Pair<T>::load(w + i, wa, wb);
+      row[i] = a * wa;
+      row[i + 1] = b * wb;
+      ss = fmaf(a, a, fmaf(b, b, ss));
+    }
+  } else {
+    for (int i = lane; i < d; i += 32) {
+      const float v = to_float(x[i]);
+      row[i] = w ? v * to_float(w[i]) : v;
+      ss = fmaf(v, v, ss);
+    }
   }
   const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
   __syncwarp();
   const int half = rotary_dim >> 1;
-  for (int i = lane; i < d; i += 32) {
+  auto turned = [&](int i) {
     float y = row[i] * rstd;
     if (i < rotary_dim) {
       const float yp = row[i < half ? i + half : i - half] * rstd;
@@ -38,7 +72,12 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
       const float c = cos_t[f], s = sin_t[f];
       y = i < half ? y * c - yp * s : y * c + yp * s;
     }
-    dst[i] = from_float<T>(y);
+    return y;
+  };
+  if (pairs) {
+    for (int i = 2 * lane; i < d; i += 64) Pair<T>::store(dst + i, turned(i), turned(i + 1));
+  } else {
+    for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(turned(i));
   }
 }
 
@@ -76,7 +115,15 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const int g = job - heads - kv_heads;
   const T* src = v_in + (size_t)t * v_stride + g * dv;
   T* dst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dv;
-  for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+  if ((dv & 1) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & Pair<T>::MASK) == 0) {
+    for (int i = 2 * lane; i < dv; i += 64) {
+      float a, b;
+      Pair<T>::load(src + i, a, b);
+      Pair<T>::store(dst + i, a, b);
+    }
+  } else {
+    for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+  }
 }
 
 }  // namespace ts
