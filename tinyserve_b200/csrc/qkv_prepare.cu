@@ -44,27 +44,71 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
                                                  int rotary_dim, int d, T* __restrict__ dst, int lane,
                                                  float* __restrict__ row) {
   const bool pairs = (d & 1) == 0 && ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w)) & Pair<T>::MASK) == 0;
+  const int half = rotary_dim >> 1;
   float ss = 0.f;
   if (pairs) {
-    for (int i = 2 * lane; i < d; i += 64) {
-      float a, b, wa = 1.f, wb = 1.f;
-      Pair<T>::load(x + i, a, b);
-      if (w) Pair<T>::load(w + i, wa, wb);
-      row[i] = a * wa;
-      row[i + 1] = b * wb;
-      ss = fmaf(a, a, fmaf(b, b, ss));
+    // everything this lane needs from global memory is asked for before anything is used: its pairs of
+    // the head, of the weight, and the angles of its elements (QP_MAX_DIM / 64 pairs at most)
+    constexpr int J = QP_MAX_DIM / 64;
+    float a[J], b[J], wa[J], wb[J], c0[J], s0[J], c1[J], s1[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int i = 2 * lane + 64 * j;
+      a[j] = b[j] = 0.f;
+      wa[j] = wb[j] = c0[j] = c1[j] = 1.f;
+      s0[j] = s1[j] = 0.f;
+      if (i < d) {
+        Pair<T>::load(x + i, a[j], b[j]);
+        if (w) Pair<T>::load(w + i, wa[j], wb[j]);
+        if (i < rotary_dim) {
+          const int f = i < half ? i : i - half;
+          c0[j] = cos_t[f];
+          s0[j] = sin_t[f];
+        }
+        if (i + 1 < rotary_dim) {
+          const int f = i + 1 < half ? i + 1 : i + 1 - half;
+          c1[j] = cos_t[f];
+          s1[j] = sin_t[f];
+        }
+      }
     }
-  } else {
-    for (int i = lane; i < d; i += 32) {
-      const float v = to_float(x[i]);
-      row[i] = w ? v * to_float(w[i]) : v;
-      ss = fmaf(v, v, ss);
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int i = 2 * lane + 64 * j;
+      if (i < d) {
+        row[i] = a[j] * wa[j];
+        row[i + 1] = b[j] * wb[j];
+        ss = fmaf(a[j], a[j], fmaf(b[j], b[j], ss));
+      }
     }
+    const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int i = 2 * lane + 64 * j;
+      if (i < d) {
+        float y0 = row[i] * rstd, y1 = row[i + 1] * rstd;
+        if (i < rotary_dim) {
+          const float p = row[i < half ? i + half : i - half] * rstd;
+          y0 = i < half ? y0 * c0[j] - p * s0[j] : y0 * c0[j] + p * s0[j];
+        }
+        if (i + 1 < rotary_dim) {
+          const float p = row[i + 1 < half ? i + 1 + half : i + 1 - half] * rstd;
+          y1 = i + 1 < half ? y1 * c1[j] - p * s1[j] : y1 * c1[j] + p * s1[j];
+        }
+        Pair<T>::store(dst + i, y0, y1);
+      }
+    }
+    return;
+  }
+  for (int i = lane; i < d; i += 32) {
+    const float v = to_float(x[i]);
+    row[i] = w ? v * to_float(w[i]) : v;
+    ss = fmaf(v, v, ss);
   }
   const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
   __syncwarp();
-  const int half = rotary_dim >> 1;
-  auto turned = [&](int i) {
+  for (int i = lane; i < d; i += 32) {
     float y = row[i] * rstd;
     if (i < rotary_dim) {
       const float yp = row[i < half ? i + half : i - half] * rstd;
@@ -72,12 +116,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
       const float c = cos_t[f], s = sin_t[f];
       y = i < half ? y * c - yp * s : y * c + yp * s;
     }
-    return y;
-  };
-  if (pairs) {
-    for (int i = 2 * lane; i < d; i += 64) Pair<T>::store(dst + i, turned(i), turned(i + 1));
-  } else {
-    for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(turned(i));
+    dst[i] = from_float<T>(y);
   }
 }
 
