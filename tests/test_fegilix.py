@@ -85,6 +85,15 @@ def test_ranks_come_from_the_checkpoint(folders, tmp_path) -> None:
         DecoderModel.from_folder(tmp_path, torch.float32, "cpu")
 
 
+def test_random_weights_need_the_ranks(tmp_path) -> None:
+    from tinyserve_b200.weights import write_random_model
+
+    cfg = json.loads(json.dumps(CONFIG_A))
+    cfg["layers"][0]["mixer"].pop("step_rank")
+    with pytest.raises(ValueError, match="only a checkpoint gives"):
+        write_random_model(tmp_path, config_from_dict(cfg), 0)
+
+
 # --------------------------------------------- references against the plain mechanisms
 def _rand(*shape, seed=0, scale=1.0):
     return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale

@@ -30,6 +30,8 @@ def _seed_for(seed: int, name: str) -> int:
 
 def _draw(name: str, shape: tuple[int, ...], init: str, std: float, seed: int,
           device: torch.device | str) -> torch.Tensor:
+    if any(n < 0 for n in shape):
+        raise ValueError(f"{name}: a size that only a checkpoint gives ({shape}); name it in the configuration to draw the tensor at random")
     g = torch.Generator(device=device).manual_seed(_seed_for(seed, name))
     t = torch.randn(shape, generator=g, dtype=torch.float32, device=device) * std
     if init == "one_plus_normal":
