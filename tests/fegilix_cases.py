@@ -55,7 +55,22 @@ CONFIG_C = {
     ],
 }
 
-CONFIGS = {"A": (CONFIG_A, 11), "B": (CONFIG_B, 12), "C": (CONFIG_C, 13)}
+# Sizes at which bfloat16 attention runs on the tensor cores (equal key and value sizes of 64, grouped heads),
+# four lanes, two layers that read the keys and values of one earlier layer, the recurrent layers last.
+ATTN_D = {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"dims": 32, "base": 5000.0, "scaling": SCALING}}
+CONFIG_D = {
+    "architecture": "Fegilix", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "streams": 4, "logit_softcap": 25.0,
+    "layers": [
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 256}, "mixer": dict(ATTN_D)},
+        {"type": "attention", "mlp": None, "mixer": {**ATTN_D, "kv_from": 0}},
+        {"type": "channel_delta", "mlp": None,
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 64, "conv": 4, "step_rank": 16, "gate_rank": 16}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 256}, "mixer": {**ATTN_D, "kv_from": 0}},
+        {"type": "mlstm", "mlp": None, "mixer": {"heads": 2, "dim": 64, "vdim": 64, "gate_cap": 12.0}},
+    ],
+}
+
+CONFIGS = {"A": (CONFIG_A, 11), "B": (CONFIG_B, 12), "C": (CONFIG_C, 13), "D": (CONFIG_D, 14)}
 
 
 def write_model(folder: Path, which: str, std_scale: float = 6.0) -> Path:

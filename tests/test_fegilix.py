@@ -222,7 +222,7 @@ def test_reference_gates() -> None:
 
 
 # ----------------------------------------------- the engine on the host, every cut
-LENGTHS = {"A": [1, 2, 9, 37, 70], "B": [3, 33, 64], "C": [5, 18, 40]}
+LENGTHS = {"A": [1, 2, 9, 37, 70], "B": [3, 33, 64], "C": [5, 18, 40], "D": [2, 21, 50]}
 
 
 @pytest.fixture(scope="module")
@@ -235,7 +235,7 @@ def oracle(folders):
     return out
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("page", [4, 16])
 def test_engine_on_host_under_every_cut(folders, oracle, which, page) -> None:
     reqs, want = oracle[which]

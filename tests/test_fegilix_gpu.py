@@ -157,7 +157,7 @@ def test_delta_scan_kernel(heads, groups, d, dv) -> None:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, d, dv", [(2, 48, 48), (3, 16, 40), (1, 128, 64), (2, 72, 100)])
+@pytest.mark.parametrize("heads, d, dv", [(2, 48, 48), (3, 16, 40), (1, 128, 64), (2, 72, 100), (1, 256, 32)])
 def test_mlstm_scan_kernel(dtype, heads, d, dv) -> None:
     from tinyserve_b200.kernels import ops
 
@@ -225,6 +225,8 @@ def _attention_case(dtype, heads, groups, d, dv, page, lens, news, rot, sink_shi
 
         class Ctx:
             num_seqs = len(live)
+            query_lens = [counts[b] for b in live]
+            context_lens = [starts[b] + counts[b] for b in live]
             cu_query_lens = torch.tensor([0] + np.cumsum([counts[b] for b in live]).tolist(), dtype=torch.int32, device="cuda")
             context_lens_dev = torch.tensor([starts[b] + counts[b] for b in live], dtype=torch.int32, device="cuda")
             decode_seqs = torch.tensor([i for i, b in enumerate(live) if counts[b] == 1] or [0], dtype=torch.int32, device="cuda")
@@ -249,7 +251,9 @@ def _attention_case(dtype, heads, groups, d, dv, page, lens, news, rot, sink_shi
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, groups, d, dv, page, rot", [(4, 2, 32, 16, 4, 16), (6, 6, 128, 128, 16, 64), (3, 1, 24, 40, 8, 0),
-                                                              (2, 2, 64, 64, 16, 64), (8, 2, 48, 80, 32, 12)])
+                                                              (2, 2, 64, 64, 16, 64), (8, 2, 48, 80, 32, 12), (8, 2, 64, 64, 16, 32),
+                                                              (8, 4, 128, 128, 16, 128), (12, 2, 128, 128, 32, 64), (4, 1, 64, 64, 8, 0),
+                                                              (2, 1, 256, 256, 16, 64), (2, 2, 192, 96, 16, 192)])
 def test_sink_attention_kernels(dtype, heads, groups, d, dv, page, rot) -> None:
     """Prompt portions beside single decoded tokens, lengths around page borders."""
     lens, news = [page * 3 + 1, 70, page * 2, 33, 1], [1, 17, 1, 33, 1]
@@ -275,6 +279,17 @@ def test_a_far_key_carries_the_weight(dtype, far_pos, new) -> None:
         torch.testing.assert_close(out[h], value[h // (heads // groups)], atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("lens, news", [([1500, 700, 64, 3000], [1, 1, 1, 1]), ([1500, 130], [300, 130]), ([2100, 40, 900], [1, 40, 1])])
+@pytest.mark.parametrize("heads, groups, d", [(8, 2, 128), (4, 4, 64), (16, 2, 64)])
+def test_sink_attention_on_the_tensor_cores_long_contexts(lens, news, heads, groups, d) -> None:
+    """bfloat16 with equal key and value sizes of 64 / 128: the tcgen05 prompt kernel and the TMA decode kernel
+    (key ranges merged inside a cluster or by the last arriver) with sink logits, grouped heads and long contexts;
+    the last query of request 0 matches one key far back."""
+    got, want, *_ = _attention_case(torch.bfloat16, heads, groups, d, d, 16, lens, news, d // 2, far=(37, 3.0))
+    assert not got.isnan().any()
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+
+
 def test_a_large_sink_takes_the_weight() -> None:
     base, *_ = _attention_case(torch.float32, 4, 2, 32, 16, 8, [40, 9], [5, 1], 16)
     sunk, *_ = _attention_case(torch.float32, 4, 2, 32, 16, 8, [40, 9], [5, 1], 16, sink_shift=25.0)
@@ -287,7 +302,7 @@ def folders(tmp_path_factory):
     return {k: write_model(tmp_path_factory.mktemp("fegilix" + k), k) for k in CONFIGS}
 
 
-LENGTHS = {"A": [1, 2, 9, 37, 70, 131], "B": [3, 33, 64, 97], "C": [5, 18, 40, 150]}
+LENGTHS = {"A": [1, 2, 9, 37, 70, 131], "B": [3, 33, 64, 97], "C": [5, 18, 40, 150], "D": [2, 47, 160, 330]}
 
 
 @pytest.fixture(scope="module")
@@ -301,7 +316,7 @@ def oracle(folders):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which, page", [("A", 4), ("A", 16), ("B", 8), ("B", 16), ("C", 16), ("C", 32)])
+@pytest.mark.parametrize("which, page", [("A", 4), ("A", 16), ("B", 8), ("B", 16), ("C", 16), ("C", 32), ("D", 16), ("D", 8)])
 def test_model_under_every_cut(folders, oracle, dtype, which, page) -> None:
     from tinyserve_b200.model import DecoderModel
 
