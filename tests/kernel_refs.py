@@ -21,8 +21,8 @@ def _round(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return x.to(dtype).float()
 
 
-def embed(tokens, table, out) -> None:
-    out.copy_(table[tokens.long()].float())
+def embed(tokens, table, out, scale=1.0) -> None:
+    out.copy_(table[tokens.long()].float() * scale)
 
 
 def add_rms_norm(resid, delta, weight, eps, out, rows=None) -> None:
@@ -33,6 +33,23 @@ def add_rms_norm(resid, delta, weight, eps, out, rows=None) -> None:
             resid.copy_(x)
     n = _round(x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps), out.dtype)
     out.copy_((n * weight.float()).to(out.dtype))
+
+
+def post_norm_add_rms_norm(resid, delta, post_weight, layer_scale, post_eps, post_offset, weight, offset, eps, out,
+                           rows=None) -> None:
+    x = resid if rows is None else resid[rows.long()]
+    if delta is not None:
+        y = (delta if rows is None else delta[rows.long()]).float()
+        if post_weight is not None:
+            g = post_weight.float()
+            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps) * (1 + g if post_offset else g)
+        if layer_scale is not None:
+            y = y * layer_scale.float()
+        x = x + y
+        if rows is None:
+            resid.copy_(x)
+    g = weight.float()
+    out.copy_((x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1 + g if offset else g)).to(out.dtype))
 
 
 def rope_tables(positions, inv_freq, cos, sin) -> None:
@@ -161,9 +178,13 @@ def hc_collapse(lanes, fresh, delta, mix_prev, out_prev, rows, out) -> None:
 
 
 # ---------------------------------------------------------------------------- gates
-def act_mul(gate_up, out, activation) -> None:
+def act_mul(gate_up, out, activation, limit=0.0) -> None:
     inter = out.shape[1]
     g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    if activation == "clamped_swish":
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(1.702 * g) * (u + 1)).to(out.dtype))
+        return
     if activation == "silu":
         a = g * torch.sigmoid(g)
     else:
@@ -171,19 +192,21 @@ def act_mul(gate_up, out, activation) -> None:
     out.copy_((a * u).to(out.dtype))
 
 
-def gemm_gated(x, w_gate_up, out, arena, activation) -> None:
+def gemm_gated(x, w_gate_up, out, arena, activation, limit=0.0) -> None:
     if activation == "silu":
         gemm_swiglu(x, w_gate_up, out, arena)
         return
     gu = (x.float() @ w_gate_up.float().t())
-    act_mul(gu, out, activation)
+    if activation == "clamped_swish":
+        gu = gu.to(out.dtype)            # the product is rounded before the separate activation kernel
+    act_mul(gu, out, activation, limit)
 
 
 def softcap(logits, cap) -> None:
     logits.copy_(cap * torch.tanh(logits / cap))
 
 
-def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out) -> None:
+def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out, gate_per_head=False) -> None:
     t, heads, w = x.shape
     y = x.float()
     if normalise:
@@ -191,8 +214,94 @@ def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out) -> Non
     if weight is not None:
         y = y * (weight.float().view(heads, w) if weight_per_head else weight.float().view(1, w))
     if gate is not None:
-        y = y * torch.sigmoid(gate.float().reshape(t, heads, w))
+        y = y * torch.sigmoid(gate.float().reshape(t, heads, 1 if gate_per_head else w))
     out.copy_(y.reshape(out.shape).to(out.dtype))
+
+
+# ----------------------------------------------------------------- latent attention
+def latent_prepare(q_in, q_folded, ckr, norm_weight, eps, cos, sin, rotary_dim, interleaved, slots, cache, heads, nope,
+                   rank, rot, q_out) -> None:
+    t = q_out.shape[0]
+    if slots is not None:
+        c = ckr[:, :rank].float()
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * norm_weight.float()
+        kr = _rotate(ckr[:, rank:].float().reshape(t, 1, rot), cos, sin, rotary_dim, interleaved).reshape(t, rot)
+        cache[slots.long()] = torch.cat([c, kr], -1).to(cache.dtype)
+    qr = _rotate(q_in.float().reshape(t, heads, nope + rot)[:, :, nope:], cos, sin, rotary_dim, interleaved)
+    q_out.copy_(torch.cat([q_folded.float().transpose(0, 1), qr], -1).to(q_out.dtype))
+
+
+def latent_attention(q, cache, page_size, block_tables, ctx: Any, rank, scale, window, out) -> None:
+    t, heads, d = q.shape
+    res = torch.zeros(t, heads, rank, dtype=torch.float32, device=q.device)
+    cu = ctx.cu_query_lens.tolist()
+    lens = ctx.context_lens_dev.tolist()
+    for b in range(ctx.num_seqs):
+        r0, n, total = cu[b], cu[b + 1] - cu[b], lens[b]
+        lo = max(0, (total - n) - window + 1) if window else 0      # pages before this may be gone
+        pos = torch.arange(lo, total, device=q.device)
+        rows = cache[block_tables[b].long()[pos // page_size] * page_size + pos % page_size].float()    # [keys, D]
+        qpos = torch.arange(total - n, total, device=q.device)
+        hidden = pos[None, :] > qpos[:, None]
+        if window:
+            hidden = hidden | (pos[None, :] <= qpos[:, None] - window)
+        s = torch.einsum("ihd,jd->hij", q[r0: r0 + n].float(), rows) * scale
+        p = torch.softmax(s.masked_fill(hidden, float("-inf")), -1)
+        res[r0: r0 + n] = torch.einsum("hij,jd->ihd", p, rows[:, :rank])
+    out.copy_(res.to(out.dtype))
+
+
+def bmm(x, w, out) -> None:
+    out.copy_(torch.bmm(x.float(), w.float()).to(out.dtype))
+
+
+def transpose01(x, out) -> None:
+    out.copy_(x.transpose(0, 1))
+
+
+# -------------------------------------------------------------------------- experts
+def moe_max_tiles(num_tokens, top, experts) -> int:
+    picks = num_tokens * top
+    return max(1, min(picks, picks // 64 + experts))
+
+
+def moe_route(logits, top, counts, arena=None) -> dict:
+    """The same plan as the kernels make, with the rows of an expert in token order."""
+    t, e = logits.shape
+    # value down, index up: a stable sort of the negated logits
+    order = torch.sort(-logits.float(), dim=-1, stable=True).indices[:, :top]
+    best = torch.gather(logits.float(), 1, order)
+    weights = torch.softmax(best, -1)
+    ids = order.reshape(-1)
+    by_expert = torch.sort(ids, stable=True).indices                 # sorted row -> pick
+    row_of = torch.empty_like(by_expert)
+    row_of[by_expert] = torch.arange(ids.numel(), device=ids.device)
+    sizes = torch.bincount(ids, minlength=e)
+    offsets = torch.cat([sizes.new_zeros(1), sizes.cumsum(0)])
+    return {"top": top, "experts": e, "picks": ids.numel(), "ids": ids.int(), "weights": weights.reshape(-1),
+            "row_of": row_of.int(), "token_of": (by_expert // top).int(), "offsets": offsets.int(),
+            "max_tiles": moe_max_tiles(t, top, e)}
+
+
+def moe_gemm(x, w, out, plan, gated, gather) -> None:
+    off = plan["offsets"].tolist()
+    src = x[plan["token_of"].long()] if gather else x
+    n = out.shape[1]
+    for e in range(plan["experts"]):
+        if off[e + 1] > off[e]:
+            z = src[off[e]: off[e + 1]].float() @ w[e].float().t()
+            if gated:
+                z = z[:, :n] * torch.sigmoid(z[:, :n]) * z[:, n:]
+            out[off[e]: off[e + 1]] = z.to(out.dtype)
+
+
+def moe_combine(y, plan, shared_out, out) -> None:
+    t, top = out.shape[0], plan["top"]
+    picked = y[plan["row_of"].long()].float().reshape(t, top, -1)
+    total = (picked * plan["weights"].reshape(t, top, 1)).sum(1)
+    if shared_out is not None:
+        total = total + shared_out.float()
+    out.copy_(total.to(out.dtype))
 
 
 # ----------------------------------------------------------------- recurrent mixers
@@ -350,7 +459,9 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, st
 
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
           "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
-          "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated"]
+          "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
+          "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles",
+          "moe_route", "moe_gemm", "moe_combine"]
 
 
 @contextmanager

@@ -12,11 +12,11 @@ namespace ts {
 int g_programmatic_launch = 0;
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = float(table[tokens[t], :]).  A token id outside [0, vocab) yields a NaN row
+// out[t, :] = float(table[tokens[t], :]) * scale.  A token id outside [0, vocab) yields a NaN row
 // instead of an out-of-bounds read (the host checks ids too).
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -27,7 +27,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 // ------------------------------------------------------- residual add + RMSNorm
@@ -235,13 +235,13 @@ extern "C" int ts_timeline_read(unsigned long long* out, int cap) {
 }
 
 extern "C" int ts_embed(const int* tokens, const void* table, float* out, int num_tokens, int hidden,
-                        int vocab, int dtype, cudaStream_t stream) {
+                        int vocab, int dtype, float scale, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == TS_DTYPE_F32)
-    return launch(embed_kernel<float>, num_tokens, threads, 0, stream, tokens, (const float*)table, out, hidden, vocab);
+    return launch(embed_kernel<float>, num_tokens, threads, 0, stream, tokens, (const float*)table, out, hidden, vocab, scale);
   if (dtype == TS_DTYPE_BF16)
-    return launch(embed_kernel<bf16>, num_tokens, threads, 0, stream, tokens, (const bf16*)table, out, hidden, vocab);
+    return launch(embed_kernel<bf16>, num_tokens, threads, 0, stream, tokens, (const bf16*)table, out, hidden, vocab, scale);
   return TS_ERR_BAD_ARGUMENT;
 }
 

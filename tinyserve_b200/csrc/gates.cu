@@ -6,28 +6,35 @@
 
 namespace ts {
 
-constexpr int ACT_SILU = 0, ACT_GELU_TANH = 1;
+constexpr int ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_CLAMPED_SWISH = 2;
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z)); }
 
 template <int ACT>
 __device__ __forceinline__ float activate(float z) {
-  if (ACT == ACT_SILU) return z / (1.f + expf(-z));
+  if (ACT == ACT_SILU || ACT == ACT_CLAMPED_SWISH) return z / (1.f + expf(-z));
   // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
   const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
   return 0.5f * z * (1.f + tanhf(inner));
 }
 
 // out[t, j] = act(gate_up[t, j]) * gate_up[t, I + j]
+// ACT_CLAMPED_SWISH: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1)
 template <typename T, int ACT>
-__global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, float limit) {
   pdl_trigger();
   pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
     const int j = (int)(idx - t * inter);
     const T* row = gate_up + t * 2 * (size_t)inter;
-    out[idx] = from_float<T>(activate<ACT>(to_float(row[j])) * to_float(row[inter + j]));
+    if (ACT == ACT_CLAMPED_SWISH) {
+      const float g = fminf(to_float(row[j]), limit);
+      const float u = fminf(fmaxf(to_float(row[inter + j]), -limit), limit);
+      out[idx] = from_float<T>(g * sigmoidf(1.702f * g) * (u + 1.f));
+    } else {
+      out[idx] = from_float<T>(activate<ACT>(to_float(row[j])) * to_float(row[inter + j]));
+    }
   }
 }
 
@@ -41,11 +48,13 @@ __global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, 
 
 // One warp per (token, head): y = x / sqrt(mean(x^2) + eps) when `normalise`, times
 // weight[head * weight_head_stride + c] when a weight is given, times sigmoid(gate[t, head, c])
-// when a gate is given. x is [T, heads, width] of type IN; gate rows are `gate_stride` apart.
+// when a gate is given (`gate_per_head`: sigmoid(gate[t, head]), one value for the whole head).
+// x is [T, heads, width] of type IN; gate rows are `gate_stride` apart.
 template <typename IN, typename T>
 __global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restrict__ weight, int weight_head_stride,
                                       const T* __restrict__ gate, int gate_stride, T* __restrict__ out,
-                                      int num_tokens, int heads, int width, int normalise, float eps) {
+                                      int num_tokens, int heads, int width, int normalise, float eps,
+                                      int gate_per_head) {
   pdl_trigger();
   pdl_wait();
   const int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
@@ -62,10 +71,11 @@ __global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restr
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)width + eps);
   }
+  const float head_gate = (gate && gate_per_head) ? sigmoidf(to_float(gate[(size_t)t * gate_stride + h])) : 1.f;
   for (int c = lane; c < width; c += 32) {
-    float v = to_float(xr[c]) * rstd;
+    float v = to_float(xr[c]) * rstd * head_gate;
     if (weight) v *= to_float(weight[h * weight_head_stride + c]);
-    if (gate) v *= sigmoidf(to_float(gate[(size_t)t * gate_stride + h * width + c]));
+    if (gate && !gate_per_head) v *= sigmoidf(to_float(gate[(size_t)t * gate_stride + h * width + c]));
     out[(size_t)warp * width + c] = from_float<T>(v);
   }
 }
@@ -80,20 +90,23 @@ static int blocks_for(size_t total, int threads) {
   return (int)b;
 }
 
-extern "C" int ts_act_mul(const void* gate_up, void* out, int num_tokens, int inter, int activation, int dtype,
-                          cudaStream_t stream) {
+extern "C" int ts_act_mul(const void* gate_up, void* out, int num_tokens, int inter, int activation, float limit,
+                          int dtype, cudaStream_t stream) {
   const size_t total = (size_t)num_tokens * inter;
   if (total == 0) return 0;
-  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return TS_ERR_BAD_ARGUMENT;
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH && activation != ACT_CLAMPED_SWISH) return TS_ERR_BAD_ARGUMENT;
+  if (activation == ACT_CLAMPED_SWISH && !(limit > 0.f)) return TS_ERR_BAD_ARGUMENT;
   const int b = blocks_for(total, 256);
 #define TS_ACT_CASE(T_, ACT_) \
-  return launch(act_mul_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)gate_up, (T_*)out, inter, total)
+  return launch(act_mul_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)gate_up, (T_*)out, inter, total, limit)
   if (dtype == TS_DTYPE_F32) {
     if (activation == ACT_SILU) TS_ACT_CASE(float, ACT_SILU);
+    if (activation == ACT_CLAMPED_SWISH) TS_ACT_CASE(float, ACT_CLAMPED_SWISH);
     TS_ACT_CASE(float, ACT_GELU_TANH);
   }
   if (dtype == TS_DTYPE_BF16) {
     if (activation == ACT_SILU) TS_ACT_CASE(bf16, ACT_SILU);
+    if (activation == ACT_CLAMPED_SWISH) TS_ACT_CASE(bf16, ACT_CLAMPED_SWISH);
     TS_ACT_CASE(bf16, ACT_GELU_TANH);
   }
 #undef TS_ACT_CASE
@@ -108,18 +121,18 @@ extern "C" int ts_softcap(float* x, size_t total, float cap, cudaStream_t stream
 
 extern "C" int ts_head_norm_gate(const void* x, int x_is_f32, const void* weight, int weight_head_stride,
                                  const void* gate, int gate_stride, void* out, int num_tokens, int heads, int width,
-                                 int normalise, float eps, int dtype, cudaStream_t stream) {
+                                 int normalise, float eps, int gate_per_head, int dtype, cudaStream_t stream) {
   const size_t warps = (size_t)num_tokens * heads;
   if (warps == 0) return 0;
   const int threads = 128;
   const int b = (int)((warps * 32 + threads - 1) / threads);
   if (dtype == TS_DTYPE_F32)
     return launch(head_norm_gate_kernel<float, float>, b, threads, 0, stream, (const float*)x, (const float*)weight,
-                  weight_head_stride, (const float*)gate, gate_stride, (float*)out, num_tokens, heads, width, normalise, eps);
+                  weight_head_stride, (const float*)gate, gate_stride, (float*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
   if (dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
   if (x_is_f32)
     return launch(head_norm_gate_kernel<float, bf16>, b, threads, 0, stream, (const float*)x, (const bf16*)weight,
-                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps);
+                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
   return launch(head_norm_gate_kernel<bf16, bf16>, b, threads, 0, stream, (const bf16*)x, (const bf16*)weight,
-                weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps);
+                weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
 }

@@ -1,0 +1,397 @@
+// A routed mixture of gated feed-forward experts, without a trip to the host:
+//
+//   route    a warp per token picks the `top` largest of its E router logits (32-bit; ties go to
+//            the lower index), soft-maxes the picked logits alone, and takes a place in each picked
+//            expert's queue (an atomic counter per expert);
+//   plan     one thread turns the counters into the experts' row ranges of the sorted order and
+//            into a list of row tiles (expert, first row), and clears the counters for the next step;
+//   scatter  every (token, pick) learns its row of the sorted order; the row learns its token;
+//   products tile by tile over that list: act[row, :] = silu(x[token] Wgate_e^T) * (x[token] Wup_e^T)
+//            (the token's row of x is fetched through the list, nothing is copied), then
+//            y[row, :] = act[row, :] Wdown_e^T;
+//   combine  out[token] = sum_j weight_j y[row_j] (+ the shared expert's output), 32-bit, rounded once.
+//
+// A row's sums run over K in index order whatever its tile holds, so a token's result does not
+// depend on which other tokens share the step or on the order in which the queue places were taken.
+// Two forms of the products: CUDA cores (float, and bf16 sizes the other form does not take), and
+// mma.sync tensor-core tiles for bf16 with cp.async staging.
+#define TS_PDL_CLASS PDL_OTHER
+#include "common.cuh"
+
+namespace ts {
+
+// ------------------------------------------------------------------------- route
+__global__ void moe_route_kernel(const float* __restrict__ logits, int num_tokens, int E, int top, int* __restrict__ ids,
+                                 float* __restrict__ weights, int* __restrict__ place, int* __restrict__ counts) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (t >= num_tokens) return;
+  const float* z = logits + (size_t)t * E;
+  float prev_v = INFINITY, my_v = -INFINITY;
+  int prev_e = -1, my_e = 0;
+  for (int j = 0; j < top; ++j) {
+    // the largest element that comes after the pick before in the order (value down, index up)
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      const bool after = (v < prev_v) || (v == prev_v && e > prev_e);
+      if (after && (v > bv || (v == bv && e < be))) { bv = v; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+    }
+    if (lane == j) { my_v = bv; my_e = be; }
+    prev_v = bv;
+    prev_e = be;
+  }
+  const float head = __shfl_sync(0xffffffffu, my_v, 0);
+  const float p = lane < top ? expf(my_v - head) : 0.f;
+  const float sum = warp_sum(p);
+  if (lane < top) {
+    const bool real = my_e >= 0 && my_e < E;       // fewer finite logits than picks: the pick is dropped
+    const int e = real ? my_e : 0;
+    ids[(size_t)t * top + lane] = e;
+    weights[(size_t)t * top + lane] = real ? p / sum : 0.f;
+    place[(size_t)t * top + lane] = atomicAdd(&counts[e], 1);
+  }
+}
+
+// -------------------------------------------------------------------------- plan
+__global__ void moe_plan_kernel(int* __restrict__ counts, int E, int tile_rows, int* __restrict__ offsets,
+                                int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ num_tiles,
+                                int max_tiles) {
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int off = 0, nt = 0;
+  for (int e = 0; e < E; ++e) {
+    const int c = counts[e];
+    offsets[e] = off;
+    for (int r = 0; r < c && nt < max_tiles; r += tile_rows) {
+      tile_expert[nt] = e;
+      tile_row0[nt] = off + r;
+      ++nt;
+    }
+    off += c;
+    counts[e] = 0;
+  }
+  offsets[E] = off;
+  *num_tiles = nt;
+}
+
+// ----------------------------------------------------------------------- scatter
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ place, const int* __restrict__ offsets,
+                                   int total, int top, int* __restrict__ row_of, int* __restrict__ token_of) {
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int row = offsets[ids[idx]] + place[idx];
+  row_of[idx] = row;
+  token_of[row] = idx / top;
+}
+
+// --------------------------------------------------------- products, CUDA cores
+constexpr int SG_M = 64, SG_N = 64, SG_K = 16, SG_THREADS = 256;
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// GATED: w holds, per expert, N gate rows then N up rows; out[row, n] = silu(g) * u.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(SG_THREADS) moe_gemm_simt_kernel(
+    const T* __restrict__ x, const int* __restrict__ token_of, const T* __restrict__ w, T* __restrict__ out,
+    const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+    const int* __restrict__ num_tiles, int N, int K) {
+  __shared__ float As[SG_K][SG_M + 4];
+  __shared__ float Bs[GATED ? 2 : 1][SG_K][SG_N + 4];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= *num_tiles) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * SG_N;
+  const T* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  const int am = r0 + lrow;
+  const long long arow = am < rend ? (token_of ? token_of[am] : am) : -1;
+  float acc[GATED ? 2 : 1][4][4];
+#pragma unroll
+  for (int g = 0; g < (GATED ? 2 : 1); ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[g][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += SG_K) {
+    float av[4], bv[GATED ? 2 : 1][4];
+    const int bn = n0 + lrow;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = k0 + lk + q;
+      av[q] = (arow >= 0 && k < K) ? to_float(x[(size_t)arow * K + k]) : 0.f;
+#pragma unroll
+      for (int g = 0; g < (GATED ? 2 : 1); ++g)
+        bv[g][q] = (bn < N && k < K) ? to_float(we[((size_t)g * N + bn) * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      As[lk + q][lrow] = av[q];
+#pragma unroll
+      for (int g = 0; g < (GATED ? 2 : 1); ++g) Bs[g][lk + q][lrow] = bv[g][q];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < SG_K; ++k) {
+      float a[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int g = 0; g < (GATED ? 2 : 1); ++g) {
+        float b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Bs[g][k][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[g][i][j] = fmaf(a[i], b[j], acc[g][i][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = r0 + ty * 4 + i;
+    if (m >= rend) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[0][i][j];
+      if (GATED) v = silu_f(v) * acc[1][i][j];
+      out[(size_t)m * N + n] = from_float<T>(v);
+    }
+  }
+}
+
+// ------------------------------------------------------- products, tensor cores
+// bf16, K % 32 == 0, N % 8 == 0. A CTA of four warps takes a tile of 64 rows x 64 output columns
+// (gated: 64 gate and 64 up columns); a warp 16 rows of it. Operands come through shared memory in
+// steps of 32 along K, three steps in flight (cp.async, 16 bytes a request; rows of 80 bytes keep
+// the ldmatrix reads free of bank conflicts).
+constexpr int TG_M = 64, TG_N = 64, TG_K = 32, TG_STAGES = 3, TG_THREADS = 128, TG_LD = TG_K + 8;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(TG_THREADS) moe_gemm_mma_kernel(
+    const bf16* __restrict__ x, const int* __restrict__ token_of, const bf16* __restrict__ w, bf16* __restrict__ out,
+    const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+    const int* __restrict__ num_tiles, int N, int K) {
+  constexpr int NB = GATED ? 2 : 1;
+  extern __shared__ __align__(16) unsigned char raw[];
+  bf16* As = (bf16*)raw;                                   // [STAGES][TG_M][TG_LD]
+  bf16* Bs = As + (size_t)TG_STAGES * TG_M * TG_LD;        // [STAGES][NB][TG_N][TG_LD]
+  __shared__ long long a_rows[TG_M];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= *num_tiles) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * TG_N;
+  const bf16* we = w + (size_t)e * NB * N * K;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < TG_M) {
+    const int m = r0 + tid;
+    a_rows[tid] = m < rend ? (long long)(token_of ? token_of[m] : m) : -1;
+  }
+  __syncthreads();
+
+  auto stage_load = [&](int stage, int k0) {
+    // A: 64 rows x 4 chunks of 8 elements; B: NB x 64 rows x 4 chunks
+    for (int c = tid; c < TG_M * 4; c += TG_THREADS) {
+      const int r = c >> 2, ch = c & 3;
+      const long long ar = a_rows[r];
+      const bf16* src = x + (size_t)(ar < 0 ? 0 : ar) * K + k0 + ch * 8;
+      cp_async16(As + ((size_t)stage * TG_M + r) * TG_LD + ch * 8, src, ar >= 0);
+    }
+    for (int c = tid; c < NB * TG_N * 4; c += TG_THREADS) {
+      const int g = c / (TG_N * 4), rest = c - g * (TG_N * 4);
+      const int r = rest >> 2, ch = rest & 3;
+      const int n = n0 + r;
+      const bf16* src = we + ((size_t)g * N + (n < N ? n : 0)) * K + k0 + ch * 8;
+      cp_async16(Bs + (((size_t)stage * NB + g) * TG_N + r) * TG_LD + ch * 8, src, n < N);
+    }
+  };
+
+  float acc[NB][8][4];
+#pragma unroll
+  for (int g = 0; g < NB; ++g)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[g][j][q] = 0.f;
+
+  const int steps = K / TG_K;
+#pragma unroll
+  for (int s = 0; s < TG_STAGES - 1; ++s) {
+    if (s < steps) stage_load(s, s * TG_K);
+    cp_async_commit();
+  }
+  for (int it = 0; it < steps; ++it) {
+    cp_async_wait<TG_STAGES - 2>();
+    __syncthreads();
+    const int nxt = it + TG_STAGES - 1;
+    if (nxt < steps) stage_load(nxt % TG_STAGES, nxt * TG_K);
+    cp_async_commit();
+    const int stage = it % TG_STAGES;
+    const bf16* Asb = As + ((size_t)stage * TG_M + warp * 16) * TG_LD;
+#pragma unroll
+    for (int kk = 0; kk < TG_K; kk += 16) {
+      uint32_t afr[4];
+      // rows lane % 16, k half lane / 16
+      ldmatrix_x4(afr, Asb + (size_t)(lane & 15) * TG_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+      for (int g = 0; g < NB; ++g) {
+        const bf16* Bsb = Bs + ((size_t)stage * NB + g) * TG_N * TG_LD;
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {
+          // two n-blocks of 8 at once: matrices (n0..7, k lo), (n0..7, k hi), (n8..15, k lo), (n8..15, k hi)
+          uint32_t bfr[4];
+          const int nrow = jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int kcol = kk + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4(bfr, Bsb + (size_t)nrow * TG_LD + kcol);
+          mma_bf16(acc[g][jp * 2], afr, bfr[0], bfr[1]);
+          mma_bf16(acc[g][jp * 2 + 1], afr, bfr[2], bfr[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  // accumulator layout: rows lane / 4 and + 8, columns (lane % 4) * 2 and + 1 of each 8-wide block
+  const int mrow = r0 + warp * 16 + (lane >> 2);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = n0 + j * 8 + (lane & 3) * 2;
+    if (n >= N) continue;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = mrow + half * 8;
+      if (m >= rend) continue;
+      float v0 = acc[0][j][half * 2], v1 = acc[0][j][half * 2 + 1];
+      if (GATED) { v0 = silu_f(v0) * acc[NB - 1][j][half * 2]; v1 = silu_f(v1) * acc[NB - 1][j][half * 2 + 1]; }
+      const __nv_bfloat162 pk = __floats2bfloat162_rn(v0, v1);
+      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)m * N + n) = pk;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------- combine
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
+                                   const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = 0.f;
+    for (int j = 0; j < top; ++j)
+      v = fmaf(weights[(size_t)t * top + j], to_float(y[(size_t)row_of[(size_t)t * top + j] * hidden + c]), v);
+    if (shared_out) v += to_float(shared_out[(size_t)t * hidden + c]);
+    out[(size_t)t * hidden + c] = from_float<T>(v);
+  }
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+extern "C" int ts_moe_tile_rows() { return SG_M; }      // both product forms use tiles of 64 rows
+
+// logits [T, E] float -> ids / weights / place [T, top]; counts [E] (zero on entry, zero again after the plan);
+// offsets [E + 1]; tile_expert / tile_row0 [max_tiles]; num_tiles [1]; row_of [T * top]; token_of [T * top].
+extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top, int* ids, float* weights, int* place,
+                            int* counts, int* offsets, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
+                            int* row_of, int* token_of, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int picks = num_tokens * top;
+  const int most = picks < picks / SG_M + E ? picks : picks / SG_M + E;   // every tile has a row; an expert one ragged tile
+  if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most) return TS_ERR_BAD_ARGUMENT;
+  int st = launch(moe_route_kernel, (num_tokens * 32 + 127) / 128, 128, 0, stream, logits, num_tokens, E, top, ids,
+                  weights, place, counts);
+  if (st != 0) return st;
+  st = launch(moe_plan_kernel, 1, 32, 0, stream, counts, E, SG_M, offsets, tile_expert, tile_row0, num_tiles, max_tiles);
+  if (st != 0) return st;
+  const int total = num_tokens * top;
+  return launch(moe_scatter_kernel, (total + 255) / 256, 256, 0, stream, (const int*)ids, (const int*)place,
+                (const int*)offsets, total, top, row_of, token_of);
+}
+
+// out[row, :] for every row of the sorted order: x rows are taken through `token_of` when it is
+// given (else row by row). w is [E, N (gated: 2 N), K]. `use_mma` 0 forces the CUDA-core form.
+extern "C" int ts_moe_gemm(const void* x, const int* token_of, const void* w, void* out, const int* offsets,
+                           const int* tile_expert, const int* tile_row0, const int* num_tiles, int max_tiles, int N,
+                           int K, int gated, int dtype, int use_mma, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (dtype == TS_DTYPE_BF16 && use_mma && K % TG_K == 0 && N % 8 == 0 &&
+      (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+    const int nb = gated ? 2 : 1;
+    const size_t smem = sizeof(bf16) * (size_t)TG_STAGES * (TG_M + nb * TG_N) * TG_LD;
+    dim3 grid((N + TG_N - 1) / TG_N, max_tiles);
+    if (gated) {
+      auto kern = moe_gemm_mma_kernel<true>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      return launch(kern, grid, TG_THREADS, smem, stream, (const bf16*)x, token_of, (const bf16*)w, (bf16*)out, offsets,
+                    tile_expert, tile_row0, num_tiles, N, K);
+    }
+    auto kern = moe_gemm_mma_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return launch(kern, grid, TG_THREADS, smem, stream, (const bf16*)x, token_of, (const bf16*)w, (bf16*)out, offsets,
+                  tile_expert, tile_row0, num_tiles, N, K);
+  }
+  dim3 grid((N + SG_N - 1) / SG_N, max_tiles);
+#define TS_MOE_CASE(T_, G_)                                                                                     \
+  return launch(moe_gemm_simt_kernel<T_, G_>, grid, SG_THREADS, 0, stream, (const T_*)x, token_of, (const T_*)w, \
+                (T_*)out, offsets, tile_expert, tile_row0, num_tiles, N, K)
+  if (dtype == TS_DTYPE_F32) { if (gated) TS_MOE_CASE(float, true); TS_MOE_CASE(float, false); }
+  if (dtype == TS_DTYPE_BF16) { if (gated) TS_MOE_CASE(bf16, true); TS_MOE_CASE(bf16, false); }
+#undef TS_MOE_CASE
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+extern "C" int ts_moe_combine(const void* y, const int* row_of, const float* weights, const void* shared_out, void* out,
+                              int num_tokens, int top, int hidden, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == TS_DTYPE_F32)
+    return launch(moe_combine_kernel<float>, num_tokens, threads, 0, stream, (const float*)y, row_of, weights,
+                  (const float*)shared_out, (float*)out, top, hidden);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(moe_combine_kernel<bf16>, num_tokens, threads, 0, stream, (const bf16*)y, row_of, weights,
+                  (const bf16*)shared_out, (bf16*)out, top, hidden);
+  return TS_ERR_BAD_ARGUMENT;
+}

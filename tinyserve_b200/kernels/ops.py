@@ -28,7 +28,7 @@ class KernelError(RuntimeError):
 
 
 _SIGNATURES: dict[str, list[Any]] = {
-    "ts_embed": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_embed": [_vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
     "ts_add_rms_norm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
     "ts_rope_tables": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "ts_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
@@ -37,9 +37,10 @@ _SIGNATURES: dict[str, list[Any]] = {
                                 _f, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "ts_hc_mix_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "ts_hc_collapse": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "ts_act_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_act_mul": [_vp, _vp, _i, _i, _i, _f, _i, _vp],
     "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
-    "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
     "ts_mlstm_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
     "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_causal_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
@@ -70,6 +71,12 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_latent_prepare": [_vp, _c.c_longlong, _vp, _vp, _c.c_longlong, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i,
+                          _i, _i, _i, _vp],
+    "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp],
+    "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -180,14 +187,14 @@ def _opt(t: torch.Tensor | None, name: str, dtype: torch.dtype | None = None) ->
 
 
 # ------------------------------------------------------------------ elementwise
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t] = float32(table[tokens[t]])``; tokens int32 ``[T]``, table ``[V, h]`` dt."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """``out[t] = float32(table[tokens[t]]) * scale``; tokens int32 ``[T]``, table ``[V, h]`` dt."""
     t, h = out.shape
     if tokens.shape != (t,) or table.shape[1] != h:
         raise KernelError(f"embed: shapes {tuple(tokens.shape)}, {tuple(table.shape)}, {tuple(out.shape)}")
     _check(_fn("ts_embed")(_dev(tokens, "tokens", torch.int32), _dev(table, "table"),
                            _dev(out, "out", torch.float32), t, h, table.shape[0], _code(table.dtype),
-                           _stream()), "embed")
+                           float(scale), _stream()), "embed")
 
 
 def add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -210,6 +217,32 @@ def add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.
                                   _dev(weight, "weight", dt), _dev(out, "out"),
                                   _opt(rows, "rows", torch.int32), n, h, float(eps), _code(dt), _stream()),
            "add_rms_norm")
+
+
+def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post_weight: torch.Tensor | None,
+                           layer_scale: torch.Tensor | None, post_eps: float, post_offset: bool, weight: torch.Tensor,
+                           offset: bool, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """The residual sum with a norm on the pending sub-layer output, and the next norm, in one pass,
+    all in 32-bit: ``y = delta / sqrt(mean(delta^2) + post_eps) * gain(post_weight) * layer_scale``
+    (``post_weight`` / ``layer_scale`` ``None``: that factor is left out), ``x = resid + y``,
+    ``out = dt(x / sqrt(mean(x^2) + eps) * gain(weight))`` with ``gain(w) = 1 + w`` when the matching
+    ``offset`` flag is set, else ``w``. Without ``rows`` the sum is written back to ``resid``; with
+    ``rows`` (int32) only those rows are read and ``resid`` stays."""
+    h = resid.shape[1]
+    n = out.shape[0]
+    dt = out.dtype
+    if weight.shape != (h,) or out.shape[1] != h or (delta is not None and delta.shape != resid.shape):
+        raise KernelError("post_norm_add_rms_norm: shape mismatch")
+    for name, v in (("post_weight", post_weight), ("layer_scale", layer_scale)):
+        if v is not None and (delta is None or v.shape != (h,)):
+            raise KernelError(f"post_norm_add_rms_norm: {name} needs a pending output and one value per column")
+    if (rows is None and n != resid.shape[0]) or (rows is not None and rows.shape != (n,)):
+        raise KernelError("post_norm_add_rms_norm: out must have one row per row of resid, or per entry of rows")
+    _check(_fn("ts_post_norm_add_rms_norm")(
+        _dev(resid, "resid", torch.float32), _opt(delta, "delta", dt), _opt(post_weight, "post_weight", dt),
+        _opt(layer_scale, "layer_scale", dt), float(post_eps), int(bool(post_offset)), _dev(weight, "weight", dt),
+        int(bool(offset)), float(eps), _dev(out, "out"), _opt(rows, "rows", torch.int32), n, h, _code(dt), _stream()),
+        "post_norm_add_rms_norm")
 
 
 def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
@@ -757,7 +790,11 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     silu_mul(gate_up, out)
 
 
-def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any, activation: str) -> None:
+FUSED_ACTIVATIONS = ("silu", "gelu_tanh")      # those the fused gate/up products know
+
+
+def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any, activation: str,
+               limit: float = 0.0) -> None:
     """``out[M, I] = act(x Wgate^T) * (x Wup^T)`` with a choice of activation (``ACTIVATIONS``). "silu"
     is :func:`gemm_swiglu`. "gelu_tanh" takes the same three routes: a few bf16 rows the skinny product
     with the activation in the same pass, many bf16 rows of a wide matrix the tcgen05 product with the
@@ -773,6 +810,11 @@ def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, aren
     if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
         raise KernelError("gemm_gated: shape or dtype mismatch")
     code = ACTIVATIONS[activation]
+    if activation not in FUSED_ACTIVATIONS:
+        gate_up = arena.take((m, 2 * inter), x.dtype)
+        gemm(x, w_gate_up, gate_up)
+        act_mul(gate_up, out, activation, limit)
+        return
     if (x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0
             and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
         _check(_fn("ts_gemm_skinny_gated")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
@@ -1056,17 +1098,21 @@ def hc_collapse(lanes: torch.Tensor, fresh: torch.Tensor | None, delta: torch.Te
 
 
 # --------------------------------------------------------------------------- gates
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
 
-def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0) -> None:
     """``out[t, j] = dt(act(gate_up[t, j]) * gate_up[t, I + j])`` in 32-bit, rounded once;
-    ``activation``: "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    ``activation``: "silu", "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or
+    "clamped_swish": with ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)`` the result is
+    ``g sigmoid(1.702 g) (u + 1)``."""
     t, inter = out.shape
     if gate_up.shape != (t, 2 * inter) or gate_up.dtype != out.dtype or activation not in ACTIVATIONS:
         raise KernelError("act_mul: shape, dtype or activation")
+    if activation == "clamped_swish" and not limit > 0:
+        raise KernelError("act_mul: the clamped activation needs a positive limit")
     _check(_fn("ts_act_mul")(_dev(gate_up, "gate_up"), _dev(out, "out"), t, inter, ACTIVATIONS[activation],
-                             _code(out.dtype), _stream()), "act_mul")
+                             float(limit), _code(out.dtype), _stream()), "act_mul")
 
 
 def softcap(logits: torch.Tensor, cap: float) -> None:
@@ -1075,11 +1121,12 @@ def softcap(logits: torch.Tensor, cap: float) -> None:
 
 
 def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head: bool, gate: torch.Tensor | None,
-                   normalise: bool, eps: float, out: torch.Tensor) -> None:
+                   normalise: bool, eps: float, out: torch.Tensor, gate_per_head: bool = False) -> None:
     """Per (token, head) of ``x [T, H, w]`` (float32 or dt): divide by the root mean square over
     ``w`` (``normalise``), multiply by ``weight`` (``[H * w]`` when ``weight_per_head`` else ``[w]``
     shared by the heads) and by ``sigmoid(gate[t, h, :])`` (``gate`` dt, rows of ``H * w`` values,
-    possibly a column slice of a wider matrix); ``out [T, H * w]`` dt."""
+    possibly a column slice of a wider matrix; with ``gate_per_head`` the gate has ``H`` values a row
+    and head ``h`` is multiplied by ``sigmoid(gate[t, h])``); ``out [T, H * w]`` dt."""
     t, heads, w = x.shape
     dt = out.dtype
     if out.numel() != t * heads * w or x.dtype not in (torch.float32, dt):
@@ -1088,13 +1135,13 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head
         raise KernelError("head_norm_gate: weight size")
     gate_stride = 0
     if gate is not None:
-        if gate.dtype != dt or gate.shape[0] != t or gate.shape[1] != heads * w or gate.stride(1) != 1:
-            raise KernelError("head_norm_gate: gate must be [T, H * w] dt with unit column stride")
+        if gate.dtype != dt or gate.shape[0] != t or gate.shape[1] != (heads if gate_per_head else heads * w) or gate.stride(1) != 1:
+            raise KernelError("head_norm_gate: gate must be [T, H * w] (or [T, H]) dt with unit column stride")
         gate_stride = gate.stride(0)
     _check(_fn("ts_head_norm_gate")(
         _dev(x, "x"), int(x.dtype == torch.float32), _opt(weight, "weight", dt), w if weight_per_head else 0,
         None if gate is None else gate.data_ptr(), gate_stride, _dev(out, "out"), t, heads, w, int(bool(normalise)),
-        float(eps), _code(dt), _stream()), "head_norm_gate")
+        float(eps), int(bool(gate_per_head)), _code(dt), _stream()), "head_norm_gate")
 
 
 # ---------------------------------------------------------------- recurrent mixers
@@ -1206,6 +1253,156 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
         _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
         _opt(slots, "slots", torch.int32), _opt(k_cache, "k_cache", dt), _opt(v_cache, "v_cache", dt), page_size, t,
         heads, kv_heads, d, dv, _dev(q_out, "q_out"), _code(dt), _stream()), "qkv_prepare")
+
+
+# ------------------------------------------------------------- latent attention
+LATENT_MAX_RANK = 512
+
+
+def latent_prepare(q_in: torch.Tensor, q_folded: torch.Tensor, ckr: torch.Tensor | None, norm_weight: torch.Tensor | None,
+                   eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None, rotary_dim: int, interleaved: bool,
+                   slots: torch.Tensor | None, cache: torch.Tensor | None, heads: int, nope: int, rank: int, rot: int,
+                   q_out: torch.Tensor) -> None:
+    """Per token: the latent part ``ckr[:, :rank]`` is RMS-normed with a plain weight and the shared
+    key part ``ckr[:, rank:]`` rotated (its first ``rotary_dim`` elements), both into the cache row
+    of the token's slot (``cache [rows, rank + rot]``; nothing is written without ``slots``); the
+    query rows ``q_out [T, heads, rank + rot]`` are the folded queries ``q_folded [heads, T, rank]``
+    followed by the rotated last ``rot`` elements of each head of ``q_in [T, heads * (nope + rot)]``.
+    ``q_in`` and ``ckr`` are 2-D dt with unit column stride (column slices of a merged product)."""
+    t = q_out.shape[0]
+    dt = q_out.dtype
+    if tuple(q_out.shape) != (t, heads, rank + rot) or tuple(q_folded.shape) != (heads, t, rank) or q_folded.dtype != dt:
+        raise KernelError("latent_prepare: query shapes")
+    if q_in.dtype != dt or tuple(q_in.shape) != (t, heads * (nope + rot)) or q_in.stride(1) != 1 or not q_in.is_cuda:
+        raise KernelError("latent_prepare: q_in must be [T, heads * (nope + rot)] dt with unit column stride on the device")
+    if slots is not None:
+        if ckr is None or ckr.dtype != dt or tuple(ckr.shape) != (t, rank + rot) or ckr.stride(1) != 1 or norm_weight is None:
+            raise KernelError("latent_prepare: ckr must be [T, rank + rot] dt with unit column stride, with its norm weight")
+        if cache is None or cache.dim() != 2 or cache.shape[1] != rank + rot or cache.dtype != dt:
+            raise KernelError("latent_prepare: cache must be [rows, rank + rot] dt")
+        _check_indices("latent_prepare", None, None, 1, cache.shape[0], slots)
+    if rotary_dim and (cos is None or tuple(cos.shape) != (t, rotary_dim // 2) or tuple(sin.shape) != tuple(cos.shape)):
+        raise KernelError("latent_prepare: rotary tables missing or of the wrong shape")
+    _check(_fn("ts_latent_prepare")(
+        q_in.data_ptr(), q_in.stride(0), _dev(q_folded, "q_folded"), None if ckr is None else ckr.data_ptr(),
+        0 if ckr is None else ckr.stride(0), _opt(norm_weight, "norm_weight", dt), float(eps),
+        _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim), int(bool(interleaved)),
+        _opt(slots, "slots", torch.int32), _opt(cache, "cache", dt), _dev(q_out, "q_out"), t, heads, nope, rank, rot,
+        _code(dt), _stream()), "latent_prepare")
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_size: int, block_tables: torch.Tensor, ctx: Any,
+                     rank: int, scale: float, window: int, out: torch.Tensor) -> None:
+    """Causal attention of the query rows ``q [T, H, rank + rot]`` over each request's cached rows
+    (``cache [pages * page_size, rank + rot]``: one row per position, shared by all heads); the
+    values are the first ``rank`` elements of the keys. ``window`` 0 means all earlier positions.
+    ``out [T, H, rank]`` dt."""
+    t, heads, d = q.shape
+    dt = q.dtype
+    if cache.dtype != dt or out.dtype != dt or cache.dim() != 2 or cache.shape[1] != d or tuple(out.shape) != (t, heads, rank):
+        raise KernelError("latent_attention: shapes or dtypes")
+    if not 0 < rank <= min(d, LATENT_MAX_RANK):
+        raise KernelError(f"latent_attention: latent size {rank} must be at most {LATENT_MAX_RANK}")
+    if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
+        raise KernelError("latent_attention: block_tables must be [requests, width]")
+    _check_indices("latent_attention", block_tables, ctx, page_size, cache.shape[0] // page_size)
+    _check(_fn("ts_latent_attention")(
+        _dev(q, "q"), _dev(out, "out"), _dev(cache, "cache"), _dev(block_tables, "block_tables", torch.int32),
+        block_tables.shape[1], _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+        _dev(ctx.context_lens_dev, "context_lens", torch.int32), ctx.num_seqs, ctx.max_query_len, heads, rank, d - rank,
+        page_size, float(scale), int(window), _code(dt), _stream()), "latent_attention")
+
+
+def bmm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[b] = x[b] @ w[b]`` for ``x [B, M, K]`` (any strides), ``w [B, K, N]``, ``out [B, M, N]``
+    contiguous: the per-head products of a latent attention layer, on the vendor library as the
+    plain products of middle sizes are. float32 is true 32-bit: the reduced-precision matrix mode
+    of the library is refused."""
+    b, m, k = x.shape
+    n = w.shape[2]
+    if tuple(w.shape) != (b, k, n) or tuple(out.shape) != (b, m, n) or x.dtype != w.dtype or out.dtype != x.dtype:
+        raise KernelError("bmm: shapes or dtypes")
+    if m == 0:
+        return
+    _dev(out, "out")
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("bmm: float32 products must not run in the library's TF32 mode")
+    torch.bmm(x, w, out=out)
+
+
+def transpose01(x: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[j, i, :] = x[i, j, :]`` (both contiguous, 3-D)."""
+    a, b, c = x.shape
+    if tuple(out.shape) != (b, a, c) or out.dtype != x.dtype:
+        raise KernelError("transpose01: shapes or dtypes")
+    _dev(x, "x"), _dev(out, "out")
+    out.copy_(x.transpose(0, 1))
+
+
+# ------------------------------------------------------------------------- experts
+MOE_TILE_ROWS = 64
+MOE_TENSOR_CORES = True
+
+
+def moe_max_tiles(num_tokens: int, top: int, experts: int) -> int:
+    """The most row tiles a step's sorted order can have: every tile holds a row, and an expert at
+    most one ragged tile beyond its full ones."""
+    picks = num_tokens * top
+    return max(1, min(picks, picks // MOE_TILE_ROWS + experts))
+
+
+def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any) -> dict[str, Any]:
+    """From router logits ``[T, E]`` float32: every token's ``top`` experts (largest logits, ties to
+    the lower index), their weights (softmax over the picked logits only), and the sorted order in
+    which the products run: rows grouped by expert, cut into tiles. ``counts`` is ``[E]`` int32,
+    zero before the call and zero again after it. Returns the plan's device arrays."""
+    t, e = logits.shape
+    if not 0 < top <= min(e, 32) or counts.shape != (e,):
+        raise KernelError("moe_route: top must be between 1 and min(experts, 32); counts one per expert")
+    picks, tiles = t * top, moe_max_tiles(t, top, e)
+    ints = arena.take((4 * picks + e + 1 + 2 * tiles + 1,), torch.int32)
+    plan = {"top": top, "experts": e, "max_tiles": tiles, "picks": picks,
+            "ids": ints[:picks], "place": ints[picks: 2 * picks], "row_of": ints[2 * picks: 3 * picks],
+            "token_of": ints[3 * picks: 4 * picks], "offsets": ints[4 * picks: 4 * picks + e + 1]}
+    at = 4 * picks + e + 1
+    plan["tile_expert"], plan["tile_row0"], plan["num_tiles"] = ints[at: at + tiles], ints[at + tiles: at + 2 * tiles], ints[at + 2 * tiles:]
+    plan["weights"] = arena.take((picks,), torch.float32)
+    _check(_fn("ts_moe_route")(
+        _dev(logits, "logits", torch.float32), t, e, top, plan["ids"].data_ptr(), plan["weights"].data_ptr(),
+        plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),
+        plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), tiles,
+        plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), _stream()), "moe_route", kernels=3)
+    return plan
+
+
+def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str, Any], gated: bool, gather: bool) -> None:
+    """The experts' products over the sorted order of ``plan``: for every sorted row r of expert e,
+    ``out[r] = x_r W_e^T`` (``gated``: ``silu(x_r Wgate_e^T) * (x_r Wup_e^T)`` with ``w [E, 2 N, K]``,
+    gate rows first; else ``w [E, N, K]``). ``gather``: ``x`` is ``[T, K]`` and row r reads its
+    token's row; else ``x`` is ``[picks, K]`` in the sorted order. ``out [picks, N]`` dt."""
+    picks, n = out.shape
+    e, rows, k = w.shape
+    if picks != plan["picks"] or e != plan["experts"] or rows != (2 * n if gated else n) or x.shape[1] != k:
+        raise KernelError("moe_gemm: shapes")
+    if x.dtype != w.dtype or out.dtype != x.dtype or (not gather and x.shape[0] != picks):
+        raise KernelError("moe_gemm: dtypes, or rows of x")
+    _check(_fn("ts_moe_gemm")(
+        _dev(x, "x"), plan["token_of"].data_ptr() if gather else None, _dev(w, "w"), _dev(out, "out"),
+        plan["offsets"].data_ptr(), plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(),
+        plan["num_tiles"].data_ptr(), plan["max_tiles"], n, k, int(bool(gated)), _code(x.dtype), int(MOE_TENSOR_CORES),
+        _stream()), "moe_gemm")
+
+
+def moe_combine(y: torch.Tensor, plan: dict[str, Any], shared_out: torch.Tensor | None, out: torch.Tensor) -> None:
+    """``out[t] = dt(sum_j weight[t, j] * y[row_of[t, j]] (+ shared_out[t]))`` in 32-bit."""
+    t, h = out.shape
+    if tuple(y.shape) != (plan["picks"], h) or t * plan["top"] != plan["picks"] or y.dtype != out.dtype:
+        raise KernelError("moe_combine: shapes or dtypes")
+    if shared_out is not None and (tuple(shared_out.shape) != (t, h) or shared_out.dtype != out.dtype):
+        raise KernelError("moe_combine: the shared output must be [T, hidden] dt")
+    _check(_fn("ts_moe_combine")(_dev(y, "y"), plan["row_of"].data_ptr(), plan["weights"].data_ptr(),
+                                 _opt(shared_out, "shared_out"), _dev(out, "out"), t, plan["top"], h, _code(out.dtype),
+                                 _stream()), "moe_combine")
 
 
 # --------------------------------------------------------------------- sampling

@@ -17,8 +17,8 @@ from typing import Any, Mapping
 import torch
 
 from ..kernels import ops
-from .base import (EVERY_STEP, KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, SplitKVNeed, StepContext,
-                   TensorSpec, project, project_to_stream, register_mixer)
+from .base import (EVERY_STEP, KVCacheEntry, KVNeed, LatentNeed, LazyNormed, Mixer, ResidualStream, SplitKVNeed,
+                   StepContext, TensorSpec, project, project_to_stream, register_mixer)
 
 
 class GQAAttention(Mixer):
@@ -134,7 +134,10 @@ class GatedSinkAttention(Mixer):
     biases; optional RMSNorm of q and k per head (plain weights shared by the heads) before the
     rotation that the layer's position encoding asks for; scores ``scale * q . k``, causal; the
     softmax's denominator gets one more term per head, ``exp(sink_h)``, to which no value belongs; the
-    concatenated heads are multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``. With
+    concatenated heads are multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``. ``sink="zero"``
+    fixes every head's sink logit at 0 (one is added to the denominator; no tensor); ``gate="head"``
+    makes ``W_g`` ``[num_heads, hidden]``, one gate value for a whole head; ``window`` limits every
+    query to the last ``window`` positions, itself included. With
     ``own_kv=False`` the layer has no key/value tensors and only ever runs as a call that reads
     another call's cache. ``names`` maps the roles "q", "k", "v", "gate", "out", "q_norm",
     "k_norm", "sink" to tensor names after the prefix.
@@ -147,8 +150,15 @@ class GatedSinkAttention(Mixer):
     _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm", "sink": "sink"}
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
-                 scale: float, qk_norm: bool = True, qk_norm_eps: float = 1e-6, sink: bool = True,
-                 own_kv: bool = True, names: Mapping[str, str] | None = None) -> None:
+                 scale: float, qk_norm: bool = True, qk_norm_eps: float = 1e-6, sink: "bool | str" = True,
+                 own_kv: bool = True, names: Mapping[str, str] | None = None, window: int | None = None,
+                 gate: str = "element") -> None:
+        if sink not in (True, False, "zero"):
+            raise ValueError(f"sink={sink!r}: True (a learned logit per head), 'zero' (a fixed logit of 0) or False")
+        if gate not in ("element", "head"):
+            raise ValueError(f"gate={gate!r}: 'element' (a value per output element) or 'head' (one per head)")
+        if window is not None and window <= 0:
+            raise ValueError(f"window must be positive or None, got {window}")
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         for what, size in (("key_dim", key_dim), ("value_dim", value_dim)):
@@ -157,17 +167,21 @@ class GatedSinkAttention(Mixer):
         self.prefix, self.h = prefix, int(hidden_size)
         self.heads, self.groups, self.d, self.dv = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
         self.scale, self.qk_norm, self.eps = float(scale), bool(qk_norm), float(qk_norm_eps)
-        self.has_sink, self.own_kv = bool(sink), bool(own_kv)
+        self.has_sink, self.learned_sink, self.own_kv = bool(sink), sink is True, bool(own_kv)
+        self.window = None if window is None else int(window)
+        self.gate_per_head = gate == "head"
         self.names = {**self._NAMES, **(names or {})}
         self.q_norm_w = self.k_norm_w = self.sink = None
 
     def cache_need(self) -> "KVNeed | SplitKVNeed":
         if self.d == self.dv:
-            return KVNeed(self.groups, self.d, None)
-        return SplitKVNeed(self.groups, self.d, self.dv, None)
+            return KVNeed(self.groups, self.d, self.window)
+        return SplitKVNeed(self.groups, self.d, self.dv, self.window)
 
     def _widths(self) -> tuple[int, int, int, int]:
-        return self.heads * self.d, self.groups * self.d, self.groups * self.dv, self.heads * self.dv
+        """Rows of the q, k, v and gate products."""
+        return (self.heads * self.d, self.groups * self.d, self.groups * self.dv,
+                self.heads if self.gate_per_head else self.heads * self.dv)
 
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         p, n, h = prefix + self.prefix, self.names, self.h
@@ -177,12 +191,12 @@ class GatedSinkAttention(Mixer):
                                 merged_rows=(q, k, v, g))]
         else:
             specs = [TensorSpec(p + "qg", (q + g, h), merged_from=(p + n["q"], p + n["gate"]), merged_rows=(q, g))]
-        specs.append(TensorSpec(p + n["out"], (h, g)))
+        specs.append(TensorSpec(p + n["out"], (h, self.heads * self.dv)))
         if self.qk_norm:
             specs.append(TensorSpec(p + n["q_norm"], (self.d,), init="one_plus_normal"))
             if self.own_kv:
                 specs.append(TensorSpec(p + n["k_norm"], (self.d,), init="one_plus_normal"))
-        if self.has_sink:
+        if self.learned_sink:
             specs.append(TensorSpec(p + n["sink"], (self.heads,), std=1.0))
         return specs
 
@@ -193,8 +207,10 @@ class GatedSinkAttention(Mixer):
         if self.qk_norm:
             self.q_norm_w = tensors[p + n["q_norm"]]
             self.k_norm_w = tensors[p + n["k_norm"]] if self.own_kv else None
-        if self.has_sink:
+        if self.learned_sink:
             self.sink = tensors[p + n["sink"]].float().contiguous()
+        elif self.has_sink:
+            self.sink = torch.zeros(self.heads, dtype=torch.float32, device=self.w_o.device)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheEntry, writes_cache: bool, position: Any) -> torch.Tensor:
         if writes_cache != self.own_kv:
@@ -214,15 +230,105 @@ class GatedSinkAttention(Mixer):
                         0 if rot is None else rot.rotary_dim, group.slots if writes_cache else None,
                         cache.k if writes_cache else None, cache.v if writes_cache else None, cache.page_size,
                         self.heads, self.groups, self.d, self.dv, queries)
-        attn = arena.take((t, g), ctx.dtype)
-        ops.paged_attention(queries, cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale, 0, attn,
-                            sinks=self.sink)
-        gated = arena.take((t, g), ctx.dtype)
-        ops.head_norm_gate(attn.view(t, self.heads, self.dv), None, False, proj[:, proj.shape[1] - g:], False, 0.0, gated)
+        width = self.heads * self.dv
+        attn = arena.take((t, width), ctx.dtype)
+        ops.paged_attention(queries, cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale,
+                            self.window or 0, attn, sinks=self.sink)
+        gated = arena.take((t, width), ctx.dtype)
+        ops.head_norm_gate(attn.view(t, self.heads, self.dv), None, False, proj[:, proj.shape[1] - g:], False, 0.0, gated,
+                           gate_per_head=self.gate_per_head)
         out = arena.take((t, self.h), ctx.dtype)
         ops.gemm(gated, self.w_o, out)
         return out
 
 
+class LatentAttention(Mixer):
+    """Attention whose keys and values are made from one low-rank latent vector per token.
+
+    ``q = W_q h``, per head ``nope_dim`` unrotated then ``rope_dim`` rotated elements. ``W_dkv h`` has
+    ``rank + rope_dim`` rows: the first ``rank``, RMS-normed with a plain weight, are the latent ``c``;
+    the last ``rope_dim`` are a key part shared by all heads, rotated like the queries' (the layer's
+    position encoding; its first ``rotary_dim`` elements turn). Head a's unrotated keys are
+    ``W_uk,a c`` and its values ``W_uv,a c``; scores ``scale * (q_nope . k_nope + q_rope . k_rope)``,
+    causal (optionally only the last ``window`` positions), ordinary softmax; ``W_o`` on the heads.
+
+    Only ``[c, k_rope]`` is cached, one row per token for all heads (``LatentNeed``). The keys'
+    up-projection is folded into the queries (``q'_a = W_uk,a^T q_nope,a``, a product per head) so
+    that every head scores against the cached row itself, and the values' up-projection is applied
+    to the weighted sum of latents (another product per head): attention with one shared key/value
+    head whose values are the first ``rank`` elements of its keys. ``names`` maps the roles "q",
+    "down", "down_norm", "up_k", "up_v", "out" to tensor names after the prefix."""
+
+    recordable = EVERY_STEP
+    _NAMES = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "out": "o"}
+
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, nope_dim: int, rope_dim: int, value_dim: int,
+                 rank: int, scale: float, norm_eps: float, window: int | None = None,
+                 names: Mapping[str, str] | None = None) -> None:
+        if min(num_heads, nope_dim, value_dim, rank) <= 0 or rope_dim < 0:
+            raise ValueError("latent attention: heads, head sizes and the latent size must be positive")
+        if rank > ops.LATENT_MAX_RANK:
+            raise ValueError(f"rank={rank}: the latent attention kernel takes latents up to {ops.LATENT_MAX_RANK}")
+        if window is not None and window <= 0:
+            raise ValueError(f"window must be positive or None, got {window}")
+        self.prefix, self.h = prefix, int(hidden_size)
+        self.heads, self.dn, self.dr, self.dv, self.rank = int(num_heads), int(nope_dim), int(rope_dim), int(value_dim), int(rank)
+        self.scale, self.eps = float(scale), float(norm_eps)
+        self.window = None if window is None else int(window)
+        self.names = {**self._NAMES, **(names or {})}
+
+    def cache_need(self) -> LatentNeed:
+        return LatentNeed(self.rank + self.dr, self.window)
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, n, h = prefix + self.prefix, self.names, self.h
+        q, down = self.heads * (self.dn + self.dr), self.rank + self.dr
+        return [TensorSpec(p + "q+down", (q + down, h), merged_from=(p + n["q"], p + n["down"]), merged_rows=(q, down)),
+                TensorSpec(p + n["down_norm"], (self.rank,), init="one_plus_normal"),
+                TensorSpec(p + n["up_k"], (self.heads * self.dn, self.rank)),
+                TensorSpec(p + n["up_v"], (self.heads * self.dv, self.rank)),
+                TensorSpec(p + n["out"], (h, self.heads * self.dv))]
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = prefix + self.prefix, self.names
+        self.w_in = tensors[p + "q+down"]
+        self.norm_w = tensors[p + n["down_norm"]]
+        self.w_uk = tensors[p + n["up_k"]].view(self.heads, self.dn, self.rank)                    # [H, nope, rank]
+        self.w_uv_t = tensors[p + n["up_v"]].view(self.heads, self.dv, self.rank).transpose(1, 2)  # [H, rank, dv] (a view)
+        self.w_o = tensors[p + n["out"]]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheEntry, writes_cache: bool, position: Any) -> torch.Tensor:
+        if not writes_cache:
+            raise RuntimeError("a latent attention layer keeps a cache of its own")
+        t, arena, hd = x.shape[0], ctx.arena, self.heads
+        group = ctx.kv[cache.group]
+        qw = hd * (self.dn + self.dr)
+        proj = arena.take((t, self.w_in.shape[0]), ctx.dtype)
+        ops.gemm(x, self.w_in, proj)
+        # the keys' up-projection folded into the queries, head by head: [H, T, nope] x [H, nope, rank]
+        q_nope = proj[:, :qw].view(t, hd, self.dn + self.dr)[:, :, : self.dn].transpose(0, 1)
+        folded = arena.take((hd, t, self.rank), ctx.dtype)
+        ops.bmm(q_nope, self.w_uk, folded)
+        rot = None if position is None else position.qk_rotation()
+        queries = arena.take((t, hd, self.rank + self.dr), ctx.dtype)
+        rows = cache.k.view(-1, self.rank + self.dr)
+        ops.latent_prepare(proj[:, :qw], folded, proj[:, qw:], self.norm_w, self.eps,
+                           None if rot is None else rot.cos, None if rot is None else rot.sin,
+                           0 if rot is None else rot.rotary_dim, False if rot is None else rot.interleaved,
+                           group.slots, rows, hd, self.dn, self.rank, self.dr, queries)
+        mixed = arena.take((t, hd, self.rank), ctx.dtype)
+        ops.latent_attention(queries, rows, cache.page_size, group.block_tables, ctx, self.rank, self.scale,
+                             self.window or 0, mixed)
+        # the values' up-projection, head by head: [H, T, rank] x [H, rank, dv], then back to token-major
+        by_head = arena.take((hd, t, self.dv), ctx.dtype)
+        ops.bmm(mixed.transpose(0, 1), self.w_uv_t, by_head)
+        heads_out = arena.take((t, hd, self.dv), ctx.dtype)
+        ops.transpose01(by_head, heads_out)
+        out = arena.take((t, self.h), ctx.dtype)
+        ops.gemm(heads_out.view(t, hd * self.dv), self.w_o, out)
+        return out
+
+
 register_mixer("gqa_attention", GQAAttention)
+register_mixer("latent_attention", LatentAttention)
 register_mixer("gated_sink_attention", GatedSinkAttention)

@@ -158,6 +158,26 @@ class SplitKVNeed(PagedNeed):
 
 
 @dataclass(frozen=True)
+class LatentNeed(PagedNeed):
+    """Pages of ONE vector per token shared by all heads (a latent from which keys and values are
+    derived, followed by a rotated key part): ``width`` elements per token. Storage
+    ``[call, page, offset, width]``; the entry's ``k`` and ``v`` are the same rows."""
+
+    width: int
+    window: int | None = None
+
+    def bytes_per_token(self, element_size: int) -> int:
+        return self.width * element_size
+
+    def allocate(self, num_calls, num_pages, page_size, dtype, device):
+        return torch.zeros((num_calls, num_pages, page_size, self.width), dtype=dtype, device=device)
+
+    def entry(self, storage, call_in_group, group, page_size):
+        rows = storage[call_in_group]
+        return KVCacheEntry(group, rows, rows, page_size)
+
+
+@dataclass(frozen=True)
 class StateNeed(SlotNeed):
     """A slot of fixed size per request: ``shape`` elements of ``dtype``."""
 
@@ -247,15 +267,20 @@ class ResidualStream:
     A model with hyper-connections keeps several copies of the stream: ``lanes`` is 32-bit
     ``[S, T, hidden]`` (``None`` until the first sub-layer makes them from ``resid``, the embedding
     output), and ``connection`` holds the ``(mix [S, S], out [S])`` weights with which the pending
-    ``delta`` enters the lanes (``parts.hyper``)."""
+    ``delta`` enters the lanes (``parts.hyper``).
 
-    __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf", "lanes", "connection")
+    A layer that norms a sub-layer's output before the residual sum leaves that norm pending too:
+    ``post`` holds ``(weight, layer_scale | None, eps, unit_offset)`` with which ``delta`` is normed
+    and scaled when the next norm folds it into the stream (``parts.norm.PostRMSNorm``)."""
+
+    __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf", "lanes", "connection", "post")
 
     def __init__(self, resid: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.resid = resid
         self.delta = delta
         self.lanes: torch.Tensor | None = None
         self.connection: tuple[torch.Tensor, torch.Tensor] | None = None
+        self.post: tuple[torch.Tensor, torch.Tensor | None, float, bool] | None = None
         self.sumsq: torch.Tensor | None = None
         self.resid16: torch.Tensor | None = None
         self._sumsq_buf: torch.Tensor | None = None

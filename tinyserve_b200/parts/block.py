@@ -44,4 +44,35 @@ class PreNormBlock(Block):
             stream.sumsq = None
 
 
+class SandwichBlock(Block):
+    """A norm before and after each sub-layer: ``x += post(mixer(norm(x)))`` and, when the layer has
+    a feed-forward, ``x += post(feed_forward(norm(x)))``. The post norms (``PostRMSNorm``, which may
+    carry a layer scale) stay pending with the output and are applied by the next norm's kernel."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    optional_roles = frozenset({"feed_forward_norm", "feed_forward", "feed_forward_post_norm"})
+
+    def __init__(self, parts: Mapping[str, Part]) -> None:
+        super().__init__(parts)
+        ff = [r for r in ("feed_forward_norm", "feed_forward", "feed_forward_post_norm") if r in parts]
+        if ff and len(ff) != 3:
+            raise ValueError("a feed-forward comes with its norm and its post norm")
+        for role in ("mixer_post_norm", "feed_forward_post_norm"):
+            if role in parts and not hasattr(parts[role], "leave"):
+                raise TypeError(f"role {role!r} takes a norm that can stay pending (a 'post_rms_norm')")
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, Any], writes_cache: bool,
+                position: Any) -> None:
+        p = self.parts
+        ctx.arena.next_frame()
+        ctx.upcoming_weights = []
+        hn = p["mixer_norm"].forward(stream, ctx)
+        p["mixer_post_norm"].leave(stream, p["mixer"].forward(hn, ctx, caches.get("mixer"), writes_cache, position))
+        if "feed_forward" in p:
+            hn = p["feed_forward_norm"].forward(stream, ctx)
+            p["feed_forward_post_norm"].leave(stream, p["feed_forward"].forward(hn, ctx))
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

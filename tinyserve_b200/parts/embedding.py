@@ -16,8 +16,10 @@ from .base import EMBEDDINGS, EVERY_STEP, HEADS, Part, StepContext, TensorSpec
 class TokenEmbedding(Part):
     recordable = EVERY_STEP
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int) -> None:
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0) -> None:
+        # scale: the gathered row is multiplied by it on its way into the 32-bit stream
         self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
+        self.scale = float(scale)
         self.table: torch.Tensor | None = None
 
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
@@ -29,7 +31,7 @@ class TokenEmbedding(Part):
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """The 32-bit residual stream ``[T, hidden]`` of this step's tokens."""
         out = ctx.arena.take((ctx.num_tokens, self.hidden_size), torch.float32)
-        ops.embed(ctx.tokens, self.table, out)
+        ops.embed(ctx.tokens, self.table, out, self.scale)
         return out
 
 

@@ -55,7 +55,9 @@ class SwiGLU(FeedForward):
 
 class GatedMLP(FeedForward):
     """``y = (act(x Wgate^T) * (x Wup^T)) Wdown^T`` with a choice of activation ("silu",
-    "gelu_tanh": ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``) and of tensor names
+    "gelu_tanh": ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``; "clamped_swish" with its
+    ``limit``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``g sigmoid(1.702 g) (u + 1)``
+    in place of ``act(gate) * up``) and of tensor names
     (``names``: role "gate" / "up" / "down" -> name after the prefix). Gate and up come from one
     product with the merged matrix, with the activation in the same kernel where the framework
     has one for the step's shape (``ops.gemm_gated``)."""
@@ -63,10 +65,12 @@ class GatedMLP(FeedForward):
     recordable = EVERY_STEP
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 names: "Mapping[str, str] | None" = None) -> None:
+                 names: "Mapping[str, str] | None" = None, limit: float | None = None) -> None:
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
-        self.prefix, self.activation = prefix, activation
+        if (activation == "clamped_swish") != (limit is not None) or (limit is not None and not limit > 0):
+            raise ValueError("'clamped_swish' takes a positive limit, the other activations none")
+        self.prefix, self.activation, self.limit = prefix, activation, 0.0 if limit is None else float(limit)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.w_gate_up = self.w_down = None
@@ -88,11 +92,90 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         t = x.shape[0]
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        ops.gemm_gated(x, self.w_gate_up, act, ctx.arena, self.activation)
+        ops.gemm_gated(x, self.w_gate_up, act, ctx.arena, self.activation, self.limit)
         out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
         ops.gemm(act, self.w_down, out)
         return out
 
 
+class RoutedExperts(FeedForward):
+    """A mixture of ``num_experts`` small SwiGLU feed-forwards of which each token uses ``top``.
+
+    Router logits ``z = W_router x`` are 32-bit; the ``top`` experts with the largest logits are
+    chosen (ties to the lower index) and weighted by the softmax over the chosen logits only; the
+    output is the weighted sum of ``W_down,e (silu(W_gate,e x) * (W_up,e x))`` over the chosen
+    experts, plus, with ``shared_size``, a SwiGLU expert of that inner size that every token uses.
+    Experts have no biases. Tensor names after the prefix: ``router``, ``e<i>.gate|up|down``,
+    ``shared.gate|up|down`` (``names`` renames "router", "expert" (a format of the index), "shared",
+    "gate", "up", "down").
+
+    The experts' matrices are stacked (``[E, 2 ff, hidden]`` gate rows then up rows, ``[E, hidden,
+    ff]``); tokens are sorted by expert on the device and the products run tile by tile over that
+    order (``ops.moe_route`` / ``moe_gemm`` / ``moe_combine``), so a step is the same launches
+    whatever the routing and can be recorded."""
+
+    recordable = EVERY_STEP
+    _NAMES = {"router": "router", "expert": "e{}.", "shared": "shared.", "gate": "gate", "up": "up", "down": "down"}
+
+    def __init__(self, prefix: str, hidden_size: int, num_experts: int, top: int, expert_size: int,
+                 shared_size: int | None = None, names: "Mapping[str, str] | None" = None) -> None:
+        if not 0 < top <= min(num_experts, 32):
+            raise ValueError(f"top={top} must be between 1 and min(num_experts={num_experts}, 32)")
+        if expert_size <= 0 or (shared_size is not None and shared_size <= 0):
+            raise ValueError("expert sizes must be positive")
+        self.prefix, self.h = prefix, int(hidden_size)
+        self.experts, self.top, self.ff = int(num_experts), int(top), int(expert_size)
+        self.shared_ff = None if shared_size is None else int(shared_size)
+        self.names = {**self._NAMES, **(names or {})}
+        self.counts: torch.Tensor | None = None
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, n, h, ff, e = prefix + self.prefix, self.names, self.h, self.ff, self.experts
+        each = [p + n["expert"].format(i) for i in range(e)]
+        specs = [TensorSpec(p + n["router"], (e, h)),
+                 TensorSpec(p + "experts.gate+up", (e * 2 * ff, h),
+                            merged_from=tuple(x + n[r] for x in each for r in ("gate", "up")), merged_rows=(ff,) * (2 * e)),
+                 TensorSpec(p + "experts.down", (e * h, ff), merged_from=tuple(x + n["down"] for x in each),
+                            merged_rows=(h,) * e)]
+        if self.shared_ff is not None:
+            sp, sf = p + n["shared"], self.shared_ff
+            specs += [TensorSpec(sp + n["gate"] + "+" + n["up"], (2 * sf, h), merged_from=(sp + n["gate"], sp + n["up"]),
+                                 merged_rows=(sf, sf)),
+                      TensorSpec(sp + n["down"], (h, sf))]
+        return specs
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = prefix + self.prefix, self.names
+        self.w_router = tensors[p + n["router"]]
+        self.w_gate_up = tensors[p + "experts.gate+up"].view(self.experts, 2 * self.ff, self.h)
+        self.w_down = tensors[p + "experts.down"].view(self.experts, self.h, self.ff)
+        if self.shared_ff is not None:
+            sp = p + n["shared"]
+            self.ws_gate_up = tensors[sp + n["gate"] + "+" + n["up"]]
+            self.ws_down = tensors[sp + n["down"]]
+        # the experts' queue counters: zero between steps (the planning kernel clears them)
+        self.counts = torch.zeros(self.experts, dtype=torch.int32, device=self.w_router.device)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        t, arena = x.shape[0], ctx.arena
+        logits = arena.take((t, self.experts), torch.float32)
+        ops.gemm(x, self.w_router, logits)
+        plan = ops.moe_route(logits, self.top, self.counts, arena)
+        act = arena.take((t * self.top, self.ff), ctx.dtype)
+        ops.moe_gemm(x, self.w_gate_up, act, plan, gated=True, gather=True)
+        y = arena.take((t * self.top, self.h), ctx.dtype)
+        ops.moe_gemm(act, self.w_down, y, plan, gated=False, gather=False)
+        shared = None
+        if self.shared_ff is not None:
+            sact = arena.take((t, self.shared_ff), ctx.dtype)
+            ops.gemm_gated(x, self.ws_gate_up, sact, arena, "silu")
+            shared = arena.take((t, self.h), ctx.dtype)
+            ops.gemm(sact, self.ws_down, shared)
+        out = arena.take((t, self.h), ctx.dtype)
+        ops.moe_combine(y, plan, shared, out)
+        return out
+
+
+register_feed_forward("routed_experts", RoutedExperts)
 register_feed_forward("swiglu", SwiGLU)
 register_feed_forward("gated_mlp", GatedMLP)
