@@ -197,8 +197,6 @@ def gemm_gated(x, w_gate_up, out, arena, activation, limit=0.0) -> None:
         gemm_swiglu(x, w_gate_up, out, arena)
         return
     gu = (x.float() @ w_gate_up.float().t())
-    if activation == "clamped_swish":
-        gu = gu.to(out.dtype)            # the product is rounded before the separate activation kernel
     act_mul(gu, out, activation, limit)
 
 

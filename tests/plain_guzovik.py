@@ -187,3 +187,11 @@ def forward(cfg: Mapping[str, Any], w: Mapping[str, torch.Tensor], tokens: list[
         after.append(x)
     logits = offset_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if keep_layers else logits
+
+
+def greedy(cfg: Mapping[str, Any], w: Mapping[str, torch.Tensor], prompt: list[int], new_tokens: int) -> list[int]:
+    """The ``new_tokens`` most likely next tokens, one after the other (the whole sequence is run again each time)."""
+    seq = list(prompt)
+    for _ in range(new_tokens):
+        seq.append(int(forward(cfg, w, seq)[-1].argmax()))
+    return seq[len(prompt):]

@@ -42,7 +42,14 @@ namespace ts {
 
 // FUSE as a template argument: 0 = a plain product, 1 = silu(gate) * up with the rounding points of the
 // separate kernels, FUSE_GELU_TANH = gelu_tanh(gate) * up in 32-bit, rounded once.
-constexpr int FUSE_GELU_TANH = 2;
+// FUSE_CLAMPED_SWISH = with g = min(gate, limit), u = clamp(up, -limit, limit): g sigmoid(1.702 g) (u + 1)
+// in 32-bit, rounded once; the limit travels in SkinnyNorm::act_limit.
+constexpr int FUSE_GELU_TANH = 2, FUSE_CLAMPED_SWISH = 3;
+__device__ __forceinline__ float clamped_swish_f(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
 }
@@ -94,6 +101,7 @@ struct SkinnyNorm {
   float* resid_out;       // RESID: [M, N] the 32-bit stream, added to in place
   bf16* resid16_out;      // RESID: [M, N] its bf16 copy
   float* sumsq_out;       // RESID: [M][N / 16]
+  float act_limit;        // FUSE_CLAMPED_SWISH: the limit
 };
 
 __device__ __forceinline__ uint4 ld_cg(const void* p) {
@@ -329,6 +337,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
         // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
         if constexpr (FUSE == FUSE_GELU_TANH) {
           out[(size_t)m * N + n0 + row] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
+        } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
+          out[(size_t)m * N + n0 + row] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
         } else {
           const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
           const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
@@ -365,7 +375,11 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
         s *= rstd_s[m];
         u *= rstd_s[m];
       }
-      if constexpr (FUSE) {
+      if constexpr (FUSE == FUSE_GELU_TANH) {
+        out[(size_t)m * N + n0 + row] = from_float<TOut>(gelu_tanh_f(s) * u);
+      } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
+        out[(size_t)m * N + n0 + row] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
+      } else if constexpr (FUSE) {
         const float gv = round_to<bf16>(s), uvv = round_to<bf16>(u);
         const float act = round_to<bf16>(gv / (1.f + expf(-gv)));
         out[(size_t)m * N + n0 + row] = from_float<TOut>(act * uvv);
@@ -717,6 +731,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
       // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
       if constexpr (FUSE == FUSE_GELU_TANH) {
         out[(size_t)om * N + n0 + orow] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
+      } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
+        out[(size_t)om * N + n0 + orow] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
       } else {
         const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
         const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
@@ -744,8 +760,10 @@ static bool to_stream_takes_h8(int M, int N, int K) {
 static bool normed_takes_h8(int M, int N, int K) { return M <= 16 && h8_spreads_better(N) && K <= SK_H8_PF * SK_H8_WARPS * 32; }
 // The plain and the SwiGLU product of up to 16 rows: narrow outputs take the tall CTAs, wide ones CTAs of 8 warps.
 template <typename TOut, int FUSE>
-static int launch_h8_plain(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
-  const SkinnyNorm nrm = SkinnyNorm();
+static int launch_h8_plain(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream,
+                           float act_limit = 0.f) {
+  SkinnyNorm nrm = SkinnyNorm();
+  nrm.act_limit = act_limit;
   if (K <= SK_H8_PF * SK_H8_WARPS * 32) {
     if (M <= 8) return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 1>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
     return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 2>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
@@ -778,8 +796,11 @@ static int dispatch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N
 }
 
 template <int NT, int FUSE = 1>
-static int dispatch_swiglu_nt(const bf16* x, const bf16* w, bf16* out, int M, int inter, int K, cudaStream_t stream) {
-  return launch_skinny<bf16, NT, 1, FUSE, 4>(x, w, out, M, inter, K, stream);
+static int dispatch_swiglu_nt(const bf16* x, const bf16* w, bf16* out, int M, int inter, int K, cudaStream_t stream,
+                              float act_limit = 0.f) {
+  SkinnyNorm nrm = SkinnyNorm();
+  nrm.act_limit = act_limit;
+  return launch_skinny<bf16, NT, 1, FUSE, 4>(x, w, out, M, inter, K, stream, nrm);
 }
 
 }  // namespace ts
@@ -815,17 +836,25 @@ extern "C" int ts_gemm_skinny_swiglu(const void* x, const void* w, void* out, in
   return dispatch_swiglu_nt<4>(xp, wp, op, M, inter, K, stream);
 }
 
-// The same with a choice of activation: 0 = silu (as above), 1 = the tanh form of GELU.
+// The same with a choice of activation: 0 = silu (as above), 1 = the tanh form of GELU, 2 = the clamped form
+// with its `limit`.
 extern "C" int ts_gemm_skinny_gated(const void* x, const void* w, void* out, int M, int inter, int K, int activation,
-                                    cudaStream_t stream) {
+                                    float limit, cudaStream_t stream) {
   if (activation == 0) return ts_gemm_skinny_swiglu(x, w, out, M, inter, K, stream);
-  if (activation != 1) return TS_ERR_BAD_ARGUMENT;
+  if (activation != 1 && activation != 2) return TS_ERR_BAD_ARGUMENT;
+  if (activation == 2 && !(limit > 0.f)) return TS_ERR_BAD_ARGUMENT;
   if (M <= 0 || inter <= 0) return 0;
   if (M > 32 || K <= 0 || K % 32 != 0 || inter % 16 != 0) return TS_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;
   bf16* op = (bf16*)out;
+  if (activation == 2) {
+    if (plain_takes_h8(M, inter, K)) return launch_h8_plain<bf16, FUSE_CLAMPED_SWISH>(xp, wp, op, M, inter, K, stream, limit);
+    if (M <= 8) return dispatch_swiglu_nt<1, FUSE_CLAMPED_SWISH>(xp, wp, op, M, inter, K, stream, limit);
+    if (M <= 16) return dispatch_swiglu_nt<2, FUSE_CLAMPED_SWISH>(xp, wp, op, M, inter, K, stream, limit);
+    return dispatch_swiglu_nt<4, FUSE_CLAMPED_SWISH>(xp, wp, op, M, inter, K, stream, limit);
+  }
   if (plain_takes_h8(M, inter, K)) return launch_h8_plain<bf16, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
   if (M <= 8) return dispatch_swiglu_nt<1, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
   if (M <= 16) return dispatch_swiglu_nt<2, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);

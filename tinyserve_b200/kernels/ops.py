@@ -69,8 +69,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
-    "ts_gemm_tcgen05_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
-    "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_gemm_tcgen05_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
     "ts_latent_prepare": [_vp, _c.c_longlong, _vp, _vp, _c.c_longlong, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i,
                           _i, _i, _i, _vp],
     "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
@@ -790,13 +790,10 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     silu_mul(gate_up, out)
 
 
-FUSED_ACTIVATIONS = ("silu", "gelu_tanh")      # those the fused gate/up products know
-
-
 def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any, activation: str,
                limit: float = 0.0) -> None:
     """``out[M, I] = act(x Wgate^T) * (x Wup^T)`` with a choice of activation (``ACTIVATIONS``). "silu"
-    is :func:`gemm_swiglu`. "gelu_tanh" takes the same three routes: a few bf16 rows the skinny product
+    is :func:`gemm_swiglu`. "gelu_tanh" and "clamped_swish" (with its ``limit``) take the same three routes: a few bf16 rows the skinny product
     with the activation in the same pass, many bf16 rows of a wide matrix the tcgen05 product with the
     activation in its epilogue, anything else a product into scratch and the activation kernel. The
     activation and the product of the halves are 32-bit, rounded once."""
@@ -810,25 +807,23 @@ def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, aren
     if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
         raise KernelError("gemm_gated: shape or dtype mismatch")
     code = ACTIVATIONS[activation]
-    if activation not in FUSED_ACTIVATIONS:
-        gate_up = arena.take((m, 2 * inter), x.dtype)
-        gemm(x, w_gate_up, gate_up)
-        act_mul(gate_up, out, activation, limit)
-        return
+    if activation == "clamped_swish" and not limit > 0:
+        raise KernelError("gemm_gated: the clamped activation needs a positive limit")
     if (x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0
             and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
         _check(_fn("ts_gemm_skinny_gated")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
-                                           code, _stream()), "gemm_gated")
+                                           code, float(limit), _stream()), "gemm_gated")
         return
     tiles = tcgen05_tiles(m, inter, 128)
     if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0 and tiles:
         _check(_fn("ts_gemm_tcgen05_gated")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
-                                            int(tiles == "pairs"), code, _error_word(x.device).data_ptr(), _stream()),
+                                            int(tiles == "pairs"), code, float(limit), _error_word(x.device).data_ptr(),
+                                            _stream()),
                "gemm_tcgen05_gated")
         return
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
-    act_mul(gate_up, out, activation)
+    act_mul(gate_up, out, activation, limit)
 
 
 # Steps of a few rows (decode) fold the RMSNorm into the products around it: the product that
