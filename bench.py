@@ -554,8 +554,9 @@ def main() -> int:
                     help="skip the batch 1 / 64 points, the prefill and the larger models")
     ap.add_argument("--skip-large", action="store_true", help="skip the points of the 8B and 32B sizes")
     ap.add_argument("--designs", action="store_true",
-                    help="instead of the headline: prefill and decode throughput of the Fegilix design beside Qwen3 at "
+                    help="instead of the headline: prefill and decode throughput of a design (--design) beside Qwen3 at "
                          "equal layer sizes (bench_designs.py); with --kernels also each step's time by kernel class")
+    ap.add_argument("--design", choices=["fegilix", "guzovik"], default="fegilix", help="with --designs: the design measured beside Qwen3")
     ap.add_argument("--design-sizes", default="", help="with --designs: layer sizes to run, e.g. 1k or 1k,4k (default: all)")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -1,8 +1,9 @@
-"""``python bench.py --designs``: prefill and decode throughput of the Fegilix design at layer
-sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder, the closest
-existing model, with the same width, attention heads, feed-forward size and number of layers; and
-where each design's step time goes, kernel class by kernel class, with the share of the measured
-peaks each class reaches. The default workload of ``bench.py`` does not come through here.
+"""``python bench.py --designs [--design fegilix|guzovik]``: prefill and decode throughput of a
+design at layer sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder,
+the closest existing model, with the same width, attention heads, (active) feed-forward size and
+number of layers; and where each design's step time goes, kernel class by kernel class, with the
+share of the measured peaks each class reaches. The default workload of ``bench.py`` does not come
+through here.
 
 The Fegilix layers follow the pattern mLSTM, mLSTM, attention + feed-forward, delta rule, mLSTM,
 attention on the third layer's keys and values + feed-forward, with two hyper-connection lanes.
@@ -17,8 +18,8 @@ from bench import PAGE, Bench, peaks
 
 SIZES = {
     # width, attention heads, kv heads, head size, feed-forward, recurrent heads
-    "1k": dict(width=1024, heads=16, kv_heads=8, dim=128, ff=3072, rec_heads=8),
-    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, rec_heads=32),
+    "1k": dict(width=1024, heads=16, kv_heads=8, dim=128, ff=3072, rec_heads=8, experts=16),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, rec_heads=32, experts=32),
 }
 VOCAB = 32768
 LAYERS = 6
@@ -45,7 +46,30 @@ def qwen3_config(s: dict) -> dict:
             "rope_theta": 1e6, "max_position_embeddings": 8192, "tie_word_embeddings": False}
 
 
-NEW_OPS = ["hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
+def guzovik_config(s: dict) -> dict:
+    """Windowed attention + clamped feed-forward, latent attention + routed experts, windowed attention +
+    routed experts, that layer again on the same tensors, a second latent layer, and the shared layer once
+    more. Three experts of a third of the dense feed-forward's size are used per token beside a shared one of
+    that size, so a token's feed-forward work equals the dense model's; latents of 512 + 64 as in large
+    models of this kind."""
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "mask": {"size": 512}}
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": 64, "vdim": s["dim"], "kv_rank": 512,
+              "scale": (s["dim"] + 64) ** -0.5, "mask": {"size": 1024}, "rot": {"dims": 64, "base": 1e6}}
+    ff = s["ff"] // 4
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": 3}, "expert": {"ff": ff}, "shared": {"ff": ff}}
+    dense = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    shared_layer = {"type": "attention", "mlp": moe, "mixer": attn, "weights_of": 2}
+    return {"architecture": "Guzovik", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "max_positions": 8192,
+            "layers": [{"type": "attention", "mlp": dense, "mixer": attn}, {"type": "latent_attention", "mlp": moe, "mixer": latent},
+                       {"type": "attention", "mlp": moe, "mixer": attn}, shared_layer,
+                       {"type": "latent_attention", "mlp": moe, "mixer": latent}, dict(shared_layer)]}
+
+
+DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config}
+NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route", "moe_gemm",
+           "moe_combine", "gemm_gated", "hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
            "causal_conv_silu", "qkv_prepare"]
 OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
            "decode_attention_fused", "gemm", "gemm_swiglu", "gemm_to_stream", "gemm_normed", "sample"]
@@ -114,19 +138,48 @@ class DesignBench(Bench):
         def nbytes(*ts) -> float:
             return float(sum(t.numel() * t.element_size() for t in ts if isinstance(t, torch.Tensor)))
 
+        def seen(ctx, window: int) -> float:
+            """(query, key) pairs of a step under a causal mask and a window (0: none)."""
+            total = 0.0
+            for n, c in zip(ctx.query_lens, ctx.context_lens):
+                for p in range(c - n, c):
+                    total += min(p + 1, window) if window else p + 1
+            return total
+
         def work(name: str, a: tuple, k: dict) -> tuple[float, float]:
             """(bytes, flops) of one call."""
-            if name in ("gemm", "gemm_swiglu", "gemm_to_stream"):
+            if name in ("gemm", "gemm_swiglu", "gemm_to_stream", "gemm_gated"):
                 return nbytes(a[0], a[1], a[2]), 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "bmm":
+                return nbytes(a[0], a[1], a[2]), 2.0 * a[0].shape[0] * a[0].shape[1] * a[0].shape[2] * a[1].shape[2]
+            if name == "moe_gemm":            # the matrices of the experts that have rows, the rows in and out
+                plan, used = a[3], min(a[3]["experts"], a[3]["picks"])
+                return (used * a[1][0].numel() * a[1].element_size() + nbytes(a[2]) + plan["picks"] * a[1].shape[2] * 2.0,
+                        2.0 * plan["picks"] * a[1].shape[1] * a[1].shape[2])
+            if name == "moe_combine":
+                return nbytes(a[0], a[2], a[3]), 0.0
+            if name == "moe_route":
+                return nbytes(a[0]) * 3.0, 0.0
+            if name == "post_norm_add_rms_norm":      # the stream read and written, the pending output, the result
+                return 2.0 * nbytes(a[0]) + nbytes(a[1], a[9]), 0.0
+            if name == "latent_prepare":
+                return nbytes(a[1], a[2]) + 2.0 * nbytes(a[15]), 0.0
+            if name == "latent_attention":    # every request's visible rows once (all heads share them)
+                ctx, rank, window, d = a[4], a[5], a[7], a[0].shape[2]
+                rows = sum(min(c, (window or c) + n - 1) for n, c in zip(ctx.query_lens, ctx.context_lens))
+                return rows * d * a[1].element_size() + nbytes(a[0], a[8]), 2.0 * a[0].shape[1] * (d + rank) * seen(ctx, window)
+            if name == "transpose01":
+                return nbytes(a[0], a[1]), 0.0
             if name == "gemm_normed":
                 return nbytes(a[0], a[4], a[5]), 2.0 * a[0].shape[0] * a[4].shape[0] * a[4].shape[1]
             if name in ("paged_attention", "decode_attention_fused"):
                 kc, vc = (a[1], a[2]) if name == "paged_attention" else (a[7], a[8])
                 ctx = a[5] if name == "paged_attention" else a[11]
                 heads = a[0].shape[1] if name == "paged_attention" else a[14]
-                pairs = sum(n * (c - n) + n * (n + 1) / 2 for n, c in zip(ctx.query_lens, ctx.context_lens))
-                return (float(sum(ctx.context_lens)) * kc.shape[1] * (kc.shape[3] + vc.shape[3]) * kc.element_size(),
-                        2.0 * heads * (kc.shape[3] + vc.shape[3]) * pairs)
+                window = a[7] if name == "paged_attention" else 0
+                rows = sum(min(c, (window or c) + n - 1) for n, c in zip(ctx.query_lens, ctx.context_lens))
+                return (float(rows) * kc.shape[1] * (kc.shape[3] + vc.shape[3]) * kc.element_size(),
+                        2.0 * heads * (kc.shape[3] + vc.shape[3]) * seen(ctx, window))
             if name == "qk_norm_rope_write":
                 return 2.0 * nbytes(a[0]), 0.0
             if name == "qkv_prepare":         # q, k and v rows read and written
@@ -224,13 +277,14 @@ def run(args) -> int:
 
     pk, pk_src = peaks()
     tokens, batch, ctx = 2048, 8, 1024
-    result = {"metric": "prefill and decode tok/s of Fegilix beside Qwen3 at equal layer sizes (6 layers, bf16, random weights)",
+    design = getattr(args, "design", "fegilix")
+    result = {"metric": f"prefill and decode tok/s of {design.capitalize()} beside Qwen3 at equal layer sizes (6 layers, bf16, random weights)",
               "peaks": {**{k: pk[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": pk_src},
               "workload": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": ctx, "page_size": PAGE}, "sizes": {}}
     for size in (args.design_sizes.split(",") if args.design_sizes else list(SIZES)):
         s = SIZES[size]
         entry = {}
-        for label, cfg in (("fegilix", fegilix_config(s)), ("qwen3", qwen3_config(s))):
+        for label, cfg in ((design, DESIGNS[design](s)), ("qwen3", qwen3_config(s))):
             b = DesignBench(cfg)
             pre = b.prefill_ms(tokens)
             dec, _, launches = b.device_decode(batch, ctx, max(args.warmup, 3), args.steps, check=False)

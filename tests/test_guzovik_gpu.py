@@ -147,13 +147,33 @@ def test_latent_attention_kernels(dtype, heads, nope, rank, rot, rotary, page, w
     torch.testing.assert_close(got, want, **_tol(dtype))
 
 
+@pytest.mark.parametrize("lens, news, window", [([1500, 700, 64, 3000], [1, 1, 1, 1], 0), ([1500, 130], [1, 1], 1024),
+                                                ([2100, 40, 900], [1, 40, 1], 300), ([5000], [1], 0), ([700, 300], [300, 130], 136)])
+@pytest.mark.parametrize("heads, rank, rot", [(16, 512, 64), (8, 128, 16), (70, 64, 32)])
+def test_latent_attention_on_the_tensor_cores_long_contexts(lens, news, window, heads, rank, rot) -> None:
+    """bfloat16 at sizes the tensor-core form takes: single tokens with their keys cut into ranges and merged,
+    prompt portions, more heads than a CTA's rows; against the reference and against the CUDA-core form."""
+    from tinyserve_b200.kernels import ops
+
+    got, want, *_ = _latent_case(torch.bfloat16, heads, 32, rank, rot, rot, 16, lens, news, window)
+    assert not got.isnan().any()
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+    ops.LATENT_TENSOR_CORES = False
+    try:
+        plain_cores, *_ = _latent_case(torch.bfloat16, heads, 32, rank, rot, rot, 16, lens, news, window)
+    finally:
+        ops.LATENT_TENSOR_CORES = True
+    torch.testing.assert_close(got, plain_cores, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("new", [1, 2, 50])
 @pytest.mark.parametrize("window", [16, 33, 100])
-def test_latent_window_edges(dtype, new, window) -> None:
+@pytest.mark.parametrize("rank, rot", [(32, 8), (64, 16)])
+def test_latent_window_edges(dtype, new, window, rank, rot) -> None:
     """The key that matches the last query stands just inside the window (it carries the weight: the
     output is its latent) or just outside (it must not be seen), in a prompt portion and decoding."""
-    heads, nope, rank, rot, page = 4, 16, 32, 8, 16
+    heads, nope, page = 4, 16, 16
     for gap, inside in ((window - 1, True), (window, False)):
         got, want, counts, store = _latent_case(dtype, heads, nope, rank, rot, 8, page, [300, 40], [new, 1], window, edge=(gap, 6.0))
         torch.testing.assert_close(got, want, **_tol(dtype))

@@ -241,6 +241,288 @@ static int launch_latent(const LatentAttnArgs& a, int max_query_len, cudaStream_
   return launch(kern, grid, LA_THREADS, smem, stream, a);
 }
 
+
+// ------------------------------------------------------- attention, tensor cores
+// bf16, (R + P) % 8 == 0, R % 16 == 0. A CTA of eight warps takes 64 query rows (a few tokens x a few
+// heads of one request; all of them score against the same cached rows) and walks over the visible
+// keys in tiles of 32, fetched with cp.async two tiles deep. Warp w owns query rows 16 (w % 4) .. + 15
+// and half of the output columns (w / 4): it forms S = Q K^T for its rows over all R + P elements
+// (mma.sync m16n8k16, operands through ldmatrix), does the online softmax in registers, and adds
+// P V to its columns, V being the first R elements of the very same rows in shared memory (read
+// transposed by ldmatrix). Both warps of a row group form the same S; that costs a third of the
+// multiply-adds again and saves exchanging P through shared memory.
+// With `splits` > 1 (steps of single tokens) a CTA takes one range of the keys and leaves an
+// unnormalised partial result; latent_merge_kernel adds the ranges up.
+constexpr int LM_THREADS = 256, LM_ROWS = 64, LM_TK = 32;
+
+__device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void lm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void lm_ldmatrix(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void lm_ldmatrix_t(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct LatentSplit {
+  int splits;
+  float* part_acc;   // [T, H, splits, R]
+  float* part_ml;    // [T, H, splits, 2]
+};
+
+// NB: blocks of 8 output columns a warp owns at most (its half of R is 8 NB columns or fewer).
+template <int NB>
+__global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(LatentAttnArgs a, LatentSplit sp, int ld) {
+  extern __shared__ __align__(16) unsigned char lm_raw[];
+  bf16* Qs = (bf16*)lm_raw;                        // [LM_ROWS][ld]
+  bf16* Ks = Qs + (size_t)LM_ROWS * ld;            // [2][LM_TK][ld]
+  pdl_trigger();
+  pdl_wait();
+  const int R = a.rank, D = a.rank + a.rot;
+  const int seq = blockIdx.y;
+  const int row0 = a.cu_q[seq];
+  const int n = a.cu_q[seq + 1] - row0;
+  const int t0 = blockIdx.x * a.tokens_per_cta;
+  if (t0 >= n) return;
+  const int nt = min(a.tokens_per_cta, n - t0);
+  const int chunk = blockIdx.z / sp.splits, split = blockIdx.z - chunk * sp.splits;
+  const int h0 = chunk * a.heads_per_cta;
+  const int nh = min(a.heads_per_cta, a.heads - h0);
+  const int nrows = nt * nh;
+  const int ctx = a.ctx_lens[seq];
+  const int first_pos = ctx - n;
+  const int* table = a.block_tables + (size_t)seq * a.table_width;
+  const bf16* q = (const bf16*)a.q;
+  const bf16* cache = (const bf16*)a.cache;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp & 3, ch = warp >> 2;
+  const int chunks = D >> 3;                       // 16-byte pieces of a row
+
+  const int qpos_first = first_pos + t0, qpos_last = first_pos + t0 + nt - 1;
+  int k_lo = a.window > 0 ? max(0, qpos_first - a.window + 1) : 0;
+  int k_hi = qpos_last + 1;
+  if (sp.splits > 1) {
+    const int per = (((k_hi - k_lo) + sp.splits - 1) / sp.splits + LM_TK - 1) / LM_TK * LM_TK;
+    k_lo = k_lo + split * per;
+    k_hi = min(k_hi, k_lo + per);
+  }
+  const int k_begin = (k_lo / LM_TK) * LM_TK;
+  const int tiles = k_hi > k_begin ? (k_hi - k_begin + LM_TK - 1) / LM_TK : 0;
+
+  auto load_tile = [&](int buf, int k0) {
+    bf16* dst = Ks + (size_t)buf * LM_TK * ld;
+    for (int c = tid; c < LM_TK * chunks; c += LM_THREADS) {
+      const int kk = c / chunks, piece = c - kk * chunks;
+      const int kpos = k0 + kk;
+      const bool ok = kpos >= k_lo && kpos < k_hi;
+      size_t crow = 0;
+      if (ok) {
+        const int pg = kpos / a.page_size;
+        crow = (size_t)table[pg] * a.page_size + (kpos - pg * a.page_size);
+      }
+      lm_cp_async16(dst + (size_t)kk * ld + piece * 8, cache + crow * D + piece * 8, ok);
+    }
+  };
+  // the queries (rows beyond the CTA's own are zero) and the first tile
+  for (int c = tid; c < LM_ROWS * chunks; c += LM_THREADS) {
+    const int r = c / chunks, piece = c - r * chunks;
+    const bool ok = r < nrows;
+    const int tt = ok ? r / nh : 0, hh = ok ? r - tt * nh : 0;
+    lm_cp_async16(Qs + (size_t)r * ld + piece * 8, q + ((size_t)(row0 + t0 + tt) * a.heads + h0 + hh) * D + piece * 8, ok);
+  }
+  if (tiles > 0) load_tile(0, k_begin);
+  lm_commit();
+
+  const int r_lo = rg * 16 + (lane >> 2), r_hi = r_lo + 8;          // this thread's two rows of the CTA
+  const int qpos_a = r_lo < nrows ? first_pos + t0 + r_lo / nh : -1;
+  const int qpos_b = r_hi < nrows ? first_pos + t0 + r_hi / nh : -1;
+  const int col_base = ch * NB * 8;                                  // first output column of this warp
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  float o[NB][4];
+#pragma unroll
+  for (int j = 0; j < NB; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+
+  for (int it = 0; it < tiles; ++it) {
+    const int k0 = k_begin + it * LM_TK;
+    if (it + 1 < tiles) load_tile((it + 1) & 1, k0 + LM_TK);
+    lm_commit();
+    lm_wait<1>();
+    __syncthreads();
+    const bf16* Kt = Ks + (size_t)(it & 1) * LM_TK * ld;
+    // ---- S = Q K^T for 16 rows x 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    const bf16* qrow = Qs + (size_t)(rg * 16 + (lane & 15)) * ld + (lane >> 4) * 8;
+    const bf16* krow = Kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8;
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t af[4], b0[4], b1[4];
+      lm_ldmatrix(af, qrow + kk);
+      lm_ldmatrix(b0, krow + kk);
+      lm_ldmatrix(b1, krow + (size_t)16 * ld + kk);
+      lm_mma(s[0], af, b0[0], b0[1]);
+      lm_mma(s[1], af, b0[2], b0[3]);
+      lm_mma(s[2], af, b1[0], b1[1]);
+      lm_mma(s[3], af, b1[2], b1[3]);
+    }
+    // ---- mask, online softmax (base 2)
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kpos = k0 + j * 8 + (lane & 3) * 2 + (e & 1);
+        const int qp = (e & 2) ? qpos_b : qpos_a;
+        bool ok = kpos >= k_lo && kpos < k_hi && kpos <= qp;
+        if (a.window > 0) ok = ok && kpos > qp - a.window;
+        const float v = ok ? s[j][e] * a.scale_log2 : -INFINITY;
+        s[j][e] = v;
+        if (e & 2) mx_b = fmaxf(mx_b, v); else mx_a = fmaxf(mx_a, v);
+      }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float corr_a = mn_a == -INFINITY ? 1.f : exp2f(m_a - mn_a);   // m = -inf gives 0
+    const float corr_b = mn_b == -INFINITY ? 1.f : exp2f(m_b - mn_b);
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mn = (e & 2) ? mn_b : mn_a;
+        const float p = s[j][e] == -INFINITY ? 0.f : exp2f(s[j][e] - mn);
+        s[j][e] = p;
+        if (e & 2) sum_b += p; else sum_a += p;
+      }
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+    l_a = l_a * corr_a + sum_a;
+    l_b = l_b * corr_b + sum_b;
+    m_a = mn_a;
+    m_b = mn_b;
+    // ---- O = O corr + P V over this warp's columns
+    uint32_t pf[2][4];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      pf[ks][0] = lm_pack(s[2 * ks][0], s[2 * ks][1]);
+      pf[ks][1] = lm_pack(s[2 * ks][2], s[2 * ks][3]);
+      pf[ks][2] = lm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      pf[ks][3] = lm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+    }
+    const bf16* vrow = Kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
+#pragma unroll
+    for (int jp = 0; jp < NB / 2; ++jp) {
+      const int col = col_base + jp * 16;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[2 * jp][e] *= (e & 2) ? corr_b : corr_a;
+        o[2 * jp + 1][e] *= (e & 2) ? corr_b : corr_a;
+      }
+      if (col < R) {                                 // warp-uniform; R % 16 == 0
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          uint32_t vf[4];
+          lm_ldmatrix_t(vf, vrow + (size_t)ks * 16 * ld + col);
+          lm_mma(o[2 * jp], pf[ks], vf[0], vf[1]);
+          lm_mma(o[2 * jp + 1], pf[ks], vf[2], vf[3]);
+        }
+      }
+    }
+    __syncthreads();       // the tile is consumed before the copy after next overwrites it
+  }
+  lm_wait<0>();
+  // ---- results: rows r_lo (e = 0, 1) and r_hi (e = 2, 3), columns col_base + 8 j + 2 (lane % 4) + (e & 1)
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r_hi : r_lo;
+    if (r >= nrows) continue;
+    const int tt = r / nh, hh = r - tt * nh;
+    const size_t orow = (size_t)(row0 + t0 + tt) * a.heads + h0 + hh;
+    const float l = half ? l_b : l_a, m = half ? m_b : m_a;
+    if (sp.splits == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* out = (bf16*)a.out + orow * R;
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const int col = col_base + j * 8 + (lane & 3) * 2;
+        if (col < R) *reinterpret_cast<__nv_bfloat162*>(out + col) = __floats2bfloat162_rn(o[j][half * 2] * inv, o[j][half * 2 + 1] * inv);
+      }
+    } else {
+      float* acc = sp.part_acc + (orow * sp.splits + split) * R;
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const int col = col_base + j * 8 + (lane & 3) * 2;
+        if (col < R) *reinterpret_cast<float2*>(acc + col) = make_float2(o[j][half * 2], o[j][half * 2 + 1]);
+      }
+      if (ch == 0 && (lane & 3) == 0) {
+        sp.part_ml[(orow * sp.splits + split) * 2] = m;
+        sp.part_ml[(orow * sp.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// out[row, :] = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s over the key ranges of a row.
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                    int splits, int R) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const float* ml = part_ml + row * splits * 2;
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ml[2 * s]);
+  float den = 0.f;
+  for (int s = 0; s < splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    float num = 0.f;
+    for (int s = 0; s < splits; ++s)
+      if (ml[2 * s] != -INFINITY) num += part_acc[(row * splits + s) * R + c] * exp2f(ml[2 * s] - mm);
+    out[row * R + c] = from_float<bf16>(num * inv);
+  }
+}
+
+template <int NB>
+static int launch_latent_mma(const LatentAttnArgs& a, const LatentSplit& sp, int max_query_len, cudaStream_t stream) {
+  const int D = a.rank + a.rot;
+  int ld = D + 8;
+  if (((ld >> 3) & 1) == 0) ld += 8;                 // rows 16 (odd) bytes apart: ldmatrix reads without bank conflicts
+  const size_t smem = sizeof(bf16) * (size_t)(LM_ROWS + 2 * LM_TK) * ld;
+  if (smem > 220 * 1024) return TS_ERR_UNSUPPORTED;
+  auto kern = latent_attention_mma_kernel<NB>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int chunks = (a.heads + a.heads_per_cta - 1) / a.heads_per_cta;
+  dim3 grid((max_query_len + a.tokens_per_cta - 1) / a.tokens_per_cta, a.num_seqs, chunks * sp.splits);
+  return launch(kern, grid, LM_THREADS, smem, stream, a, sp, ld);
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -268,16 +550,43 @@ extern "C" int ts_latent_prepare(const void* q_in, long long q_stride, const voi
 // Largest latent size the kernel takes (32 output columns per lane and step, 16 steps).
 extern "C" int ts_latent_attention_max_rank() { return 512; }
 
+// Whether the tensor-core form takes these sizes (bf16 only).
+extern "C" int ts_latent_attention_mma_takes(int rank, int rot) {
+  const int D = rank + rot;
+  int ld = D + 8;
+  if (((ld >> 3) & 1) == 0) ld += 8;
+  return rank % 16 == 0 && D % 16 == 0 && rank <= 512 && sizeof(bf16) * (size_t)(LM_ROWS + 2 * LM_TK) * ld <= 220 * 1024;
+}
+
+// `splits` > 1 (steps of single tokens, tensor-core form only): key ranges per request, with scratch
+// part_acc [T, heads, splits, rank] and part_ml [T, heads, splits, 2] floats.
 extern "C" int ts_latent_attention(const void* q, void* out, const void* cache, const int* block_tables, int table_width,
                                    const int* cu_q, const int* ctx_lens, int num_seqs, int max_query_len, int heads,
-                                   int rank, int rot, int page_size, float scale, int window, int dtype,
-                                   cudaStream_t stream) {
+                                   int rank, int rot, int page_size, float scale, int window, int dtype, int use_mma,
+                                   int splits, float* part_acc, float* part_ml, int num_tokens, cudaStream_t stream) {
   if (num_seqs <= 0 || max_query_len <= 0) return 0;
   if (heads <= 0 || rank <= 0 || rank > 512 || rot < 0 || page_size <= 0 || window < 0) return TS_ERR_BAD_ARGUMENT;
   LatentAttnArgs a;
   a.q = q; a.out = out; a.cache = cache; a.block_tables = block_tables; a.table_width = table_width;
   a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.num_seqs = num_seqs; a.heads = heads; a.rank = rank; a.rot = rot;
   a.page_size = page_size; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+  if (dtype == TS_DTYPE_BF16 && use_mma && ts_latent_attention_mma_takes(rank, rot) &&
+      (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) == 0) {
+    if (splits < 1 || (splits > 1 && (max_query_len != 1 || !part_acc || !part_ml))) return TS_ERR_BAD_ARGUMENT;
+    // 64 rows a CTA where the step has them: up to 64 heads of as many tokens as fit
+    a.heads_per_cta = heads < LM_ROWS ? heads : LM_ROWS;
+    a.tokens_per_cta = max_query_len == 1 ? 1 : (LM_ROWS / a.heads_per_cta);
+    LatentSplit sp;
+    sp.splits = splits; sp.part_acc = part_acc; sp.part_ml = part_ml;
+    const int nb = (rank / 2 + 15) / 16 * 2;        // blocks of 8 columns per half, an even number
+    int st;
+    if (nb <= 8) st = launch_latent_mma<8>(a, sp, max_query_len, stream);
+    else if (nb <= 16) st = launch_latent_mma<16>(a, sp, max_query_len, stream);
+    else st = launch_latent_mma<32>(a, sp, max_query_len, stream);
+    if (st != 0 || splits == 1) return st;
+    return launch(latent_merge_kernel, num_tokens * heads, 128, 0, stream, (const float*)part_acc, (const float*)part_ml,
+                  (bf16*)out, splits, rank);
+  }
   // 32 rows a CTA where the step has them: 8 heads of 4 tokens (a single token: 8 heads)
   a.heads_per_cta = heads < 8 ? heads : 8;
   a.tokens_per_cta = max_query_len == 1 ? 1 : (32 / a.heads_per_cta);

@@ -21,13 +21,10 @@
 namespace ts {
 
 // ------------------------------------------------------------------------- route
-__global__ void moe_route_kernel(const float* __restrict__ logits, int num_tokens, int E, int top, int* __restrict__ ids,
-                                 float* __restrict__ weights, int* __restrict__ place, int* __restrict__ counts) {
-  pdl_trigger();
-  pdl_wait();
-  const int t = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
-  if (t >= num_tokens) return;
-  const float* z = logits + (size_t)t * E;
+// One token by one warp: picks, weights, and a place in each picked expert's queue (`counts` may be
+// in shared memory).
+__device__ __forceinline__ void route_token(const float* __restrict__ z, int t, int lane, int E, int top, int* __restrict__ ids,
+                                            float* __restrict__ weights, int* __restrict__ place, int* counts) {
   float prev_v = INFINITY, my_v = -INFINITY;
   int prev_e = -1, my_e = 0;
   for (int j = 0; j < top; ++j) {
@@ -58,6 +55,56 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int num_token
     ids[(size_t)t * top + lane] = e;
     weights[(size_t)t * top + lane] = real ? p / sum : 0.f;
     place[(size_t)t * top + lane] = atomicAdd(&counts[e], 1);
+  }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int num_tokens, int E, int top, int* __restrict__ ids,
+                                 float* __restrict__ weights, int* __restrict__ place, int* __restrict__ counts) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (t >= num_tokens) return;
+  route_token(logits + (size_t)t * E, t, lane, E, top, ids, weights, place, counts);
+}
+
+// A step of few tokens (decoding): route, plan and scatter by ONE CTA, the queue counters in shared
+// memory, so that the three launches become one.
+constexpr int ROUTE_SMALL_THREADS = 512, ROUTE_SMALL_MAX_EXPERTS = 1024;
+__global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
+    const float* __restrict__ logits, int num_tokens, int E, int top, int tile_rows, int* __restrict__ ids,
+    float* __restrict__ weights, int* __restrict__ place, int* __restrict__ offsets, int* __restrict__ tile_expert,
+    int* __restrict__ tile_row0, int* __restrict__ num_tiles, int max_tiles, int* __restrict__ row_of,
+    int* __restrict__ token_of) {
+  __shared__ int counts[ROUTE_SMALL_MAX_EXPERTS];
+  __shared__ int offs[ROUTE_SMALL_MAX_EXPERTS + 1];
+  pdl_trigger();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  pdl_wait();
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int t = warp; t < num_tokens; t += warps) route_token(logits + (size_t)t * E, t, lane, E, top, ids, weights, place, counts);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = counts[e];
+      offs[e] = off;
+      offsets[e] = off;
+      for (int r = 0; r < c && nt < max_tiles; r += tile_rows) {
+        tile_expert[nt] = e;
+        tile_row0[nt] = off + r;
+        ++nt;
+      }
+      off += c;
+    }
+    offsets[E] = off;
+    *num_tiles = nt;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < num_tokens * top; idx += blockDim.x) {
+    const int row = offs[ids[idx]] + place[idx];
+    row_of[idx] = row;
+    token_of[row] = idx / top;
   }
 }
 
@@ -338,6 +385,9 @@ extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top,
   const int picks = num_tokens * top;
   const int most = picks < picks / SG_M + E ? picks : picks / SG_M + E;   // every tile has a row; an expert one ragged tile
   if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most) return TS_ERR_BAD_ARGUMENT;
+  if (num_tokens <= 64 && E <= ROUTE_SMALL_MAX_EXPERTS)
+    return launch(moe_route_small_kernel, 1, ROUTE_SMALL_THREADS, 0, stream, logits, num_tokens, E, top, SG_M, ids, weights, place,
+                  offsets, tile_expert, tile_row0, num_tiles, max_tiles, row_of, token_of);
   int st = launch(moe_route_kernel, (num_tokens * 32 + 127) / 128, 128, 0, stream, logits, num_tokens, E, top, ids,
                   weights, place, counts);
   if (st != 0) return st;

@@ -73,7 +73,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
     "ts_latent_prepare": [_vp, _c.c_longlong, _vp, _vp, _c.c_longlong, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i,
                           _i, _i, _i, _vp],
-    "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _i, _vp],
+    "ts_latent_attention_mma_takes": [_i, _i],
     "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp],
     "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -1252,6 +1253,16 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
 
 # ------------------------------------------------------------- latent attention
 LATENT_MAX_RANK = 512
+LATENT_TENSOR_CORES = True        # bf16 at sizes the mma.sync form takes; False: CUDA cores always
+LATENT_MAX_SPLITS = 16
+LATENT_MIN_KEYS_PER_SPLIT = 64
+
+
+def latent_splits(num_seqs: int, heads: int, keys: int) -> int:
+    """Key ranges per request for a step of single tokens: enough CTAs (one per request, 64 heads and
+    range) to give every SM one, no range shorter than 64 keys. Depends only on the step's shape."""
+    ctas = max(1, num_seqs * -(-heads // 64))
+    return max(1, min(SM_COUNT // ctas, keys // LATENT_MIN_KEYS_PER_SPLIT, LATENT_MAX_SPLITS))
 
 
 def latent_prepare(q_in: torch.Tensor, q_folded: torch.Tensor, ckr: torch.Tensor | None, norm_weight: torch.Tensor | None,
@@ -1301,11 +1312,20 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_size: int, block
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("latent_attention: block_tables must be [requests, width]")
     _check_indices("latent_attention", block_tables, ctx, page_size, cache.shape[0] // page_size)
+    mma = bool(LATENT_TENSOR_CORES and dt == torch.bfloat16 and _fn("ts_latent_attention_mma_takes")(rank, d - rank))
+    splits, part_acc, part_ml = 1, None, None
+    if mma and ctx.max_query_len == 1:
+        keys = min(ctx.max_context_len, window) if window else ctx.max_context_len
+        splits = latent_splits(ctx.num_seqs, heads, keys)
+        if splits > 1:
+            part_acc = ctx.arena.take((t, heads, splits, rank), torch.float32)
+            part_ml = ctx.arena.take((t, heads, splits, 2), torch.float32)
     _check(_fn("ts_latent_attention")(
         _dev(q, "q"), _dev(out, "out"), _dev(cache, "cache"), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
         _dev(ctx.context_lens_dev, "context_lens", torch.int32), ctx.num_seqs, ctx.max_query_len, heads, rank, d - rank,
-        page_size, float(scale), int(window), _code(dt), _stream()), "latent_attention")
+        page_size, float(scale), int(window), _code(dt), int(mma), splits, _opt(part_acc, "part_acc"),
+        _opt(part_ml, "part_ml"), t, _stream()), "latent_attention", kernels=2 if splits > 1 else 1)
 
 
 def bmm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -1366,7 +1386,7 @@ def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any) 
         _dev(logits, "logits", torch.float32), t, e, top, plan["ids"].data_ptr(), plan["weights"].data_ptr(),
         plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),
         plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), tiles,
-        plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), _stream()), "moe_route", kernels=3)
+        plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), _stream()), "moe_route", kernels=1 if t <= 64 else 3)
     return plan
 
 
