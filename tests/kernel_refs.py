@@ -258,12 +258,16 @@ def transpose01(x, out) -> None:
 
 
 # -------------------------------------------------------------------------- experts
-def moe_max_tiles(num_tokens, top, experts) -> int:
+def moe_max_tiles(num_tokens, top, experts, tile_rows=64) -> int:
     picks = num_tokens * top
-    return max(1, min(picks, picks // 64 + experts))
+    return max(1, min(picks, picks // tile_rows + experts))
 
 
-def moe_route(logits, top, counts, arena=None) -> dict:
+def moe_tile_rows(num_tokens, top, experts, dtype, widths) -> int:
+    return 64
+
+
+def moe_route(logits, top, counts, arena=None, tile_rows=64) -> dict:
     """The same plan as the kernels make, with the rows of an expert in token order."""
     t, e = logits.shape
     # value down, index up: a stable sort of the negated logits
@@ -278,10 +282,10 @@ def moe_route(logits, top, counts, arena=None) -> dict:
     offsets = torch.cat([sizes.new_zeros(1), sizes.cumsum(0)])
     return {"top": top, "experts": e, "picks": ids.numel(), "ids": ids.int(), "weights": weights.reshape(-1),
             "row_of": row_of.int(), "token_of": (by_expert // top).int(), "offsets": offsets.int(),
-            "max_tiles": moe_max_tiles(t, top, e)}
+            "max_tiles": moe_max_tiles(t, top, e, tile_rows), "tile_rows": tile_rows}
 
 
-def moe_gemm(x, w, out, plan, gated, gather) -> None:
+def moe_gemm(x, w, out, plan, gated, gather, arena=None) -> None:
     off = plan["offsets"].tolist()
     src = x[plan["token_of"].long()] if gather else x
     n = out.shape[1]
@@ -458,7 +462,7 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, st
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
           "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
           "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
-          "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles",
+          "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows",
           "moe_route", "moe_gemm", "moe_combine"]
 
 

@@ -357,6 +357,44 @@ def test_routed_expert_kernels(dtype, tokens, experts, top, hidden, ff, shared) 
         torch.testing.assert_close(out, out_r.float(), **_tol(dtype))
 
 
+@pytest.mark.parametrize("tokens, experts, top, hidden, ff, skip", [
+    (700, 4, 2, 256, 256, None), (2048, 16, 3, 1024, 768, 5), (1100, 3, 1, 512, 320, None), (600, 8, 8, 256, 1024, 0)])
+def test_routed_experts_on_the_tcgen05_product(tokens, experts, top, hidden, ff, skip) -> None:
+    """Steps of many rows: tiles of 128 sorted rows through the tcgen05 product, ragged experts, an expert
+    that nobody picks, rows gathered first; against the reference and against the tiles of 64."""
+    from tinyserve_b200.kernels import ops
+
+    dtype = torch.bfloat16
+    logits = _rand(tokens, experts, seed=1, scale=2.0)
+    if skip is not None and top < experts:
+        logits[:, skip] = -50.0
+    counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    assert ops.moe_tile_rows(tokens, top, experts, dtype, (hidden, ff)) == 128
+    x = _rand(tokens, hidden, seed=2, dtype=dtype)
+    w1 = _rand(experts, 2 * ff, hidden, seed=3, scale=hidden ** -0.5, dtype=dtype)
+    w2 = _rand(experts, hidden, ff, seed=4, scale=ff ** -0.5, dtype=dtype)
+    outs = []
+    for rows in (128, 64):
+        plan = ops.moe_route(logits, top, counts, Arena(), rows)
+        act = torch.full((tokens * top, ff), float("nan"), dtype=dtype, device="cuda")
+        y = torch.full((tokens * top, hidden), float("nan"), dtype=dtype, device="cuda")
+        out = torch.empty(tokens, hidden, dtype=dtype, device="cuda")
+        ops.moe_gemm(x, w1, act, plan, gated=True, gather=True, arena=Arena())
+        ops.moe_gemm(act, w2, y, plan, gated=False, gather=False, arena=Arena())
+        ops.moe_combine(y, plan, None, out)
+        ops.check_device_errors()
+        outs.append(out.float())
+    want = refs.moe_route(logits, top, None)
+    act_r, y_r, out_r = (torch.empty(tokens * top, ff, dtype=dtype, device="cuda"), torch.empty(tokens * top, hidden, dtype=dtype, device="cuda"),
+                         torch.empty(tokens, hidden, dtype=dtype, device="cuda"))
+    refs.moe_gemm(x, w1, act_r, want, True, True)
+    refs.moe_gemm(act_r, w2, y_r, want, False, False)
+    refs.moe_combine(y_r, want, None, out_r)
+    for out in outs:
+        assert not out.isnan().any()
+        torch.testing.assert_close(out, out_r.float(), atol=3e-2, rtol=3e-2)
+
+
 def test_a_token_alone_and_in_a_crowd_takes_the_same_experts_path() -> None:
     """float32: a row's sums do not depend on what shares its tile."""
     from tinyserve_b200.kernels import ops
@@ -415,6 +453,25 @@ def test_model_under_every_cut(folders, oracle, dtype, which, page) -> None:
         assert all(sorted(got[rid]) == list(range(len(reqs[rid]))) for rid in got)
         rows = torch.cat([torch.stack([got[rid][p] for p in range(len(reqs[rid]))]) for rid in got])
         assert_rows_close(rows, torch.cat([want[rid] for rid in got]), dtype, f"{which}, schedule {n}")
+
+
+def test_model_with_its_experts_on_the_tcgen05_product(folders, oracle) -> None:
+    """The thresholds lowered so that the small model's prompt portions take the tiles of 128 rows."""
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    reqs, want = oracle["D"]
+    model = DecoderModel.from_folder(folders["D"], torch.bfloat16, "cuda")
+    saved = ops.MOE_TCGEN05_MIN_ROWS, ops.MOE_TCGEN05_MIN_COLS
+    ops.MOE_TCGEN05_MIN_ROWS, ops.MOE_TCGEN05_MIN_COLS = 256, 64
+    try:
+        assert ops.moe_tile_rows(330, 2, 4, torch.bfloat16, (128, 64)) == 128
+        for steps in (cases.whole("r3", reqs["r3"]), cases.mixed(reqs, 3)):
+            got, _ = run_steps(model, 16, steps, cases.max_live_tokens(steps))
+            rows = torch.cat([torch.stack([got[rid][p] for p in range(len(reqs[rid]))]) for rid in got])
+            assert_rows_close(rows, torch.cat([want[rid] for rid in got]), torch.bfloat16, "D")
+    finally:
+        ops.MOE_TCGEN05_MIN_ROWS, ops.MOE_TCGEN05_MIN_COLS = saved
 
 
 def test_batch_mates_and_pages_do_not_matter(folders, oracle) -> None:

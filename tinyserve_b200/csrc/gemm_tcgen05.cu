@@ -120,6 +120,18 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
   }
 }
 
+// A grouped product (the experts of a routed feed-forward): the rows of x are sorted by expert, the
+// list of row tiles (expert, first row) and the experts' row ranges were made on the device, and w
+// stacks the experts' matrices, `w_rows` rows each. A tile takes 128 rows from its first row on; rows
+// beyond its expert's range are computed and not stored. `tile_expert` null: a plain product.
+struct GemmGroup {
+  const int* tile_expert = nullptr;
+  const int* tile_row0 = nullptr;
+  const int* offsets = nullptr;      // [experts + 1] first sorted row of every expert
+  const int* num_tiles = nullptr;    // [1] row tiles in the list
+  int w_rows = 0;
+};
+
 // Persistent, warp-specialised: a CTA loops over output tiles (tile = blockIdx.x + i * gridDim.x,
 // rows fastest, so CTAs that run together share weight tiles in L2). The accumulator is double-
 // buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i, the
@@ -128,7 +140,8 @@ template <int BN, int STAGES, typename TOut, int SWIGLU = false>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   TOut* __restrict__ out, int M, int N, int K,
-                                                                  int* __restrict__ error_flag, float act_limit) {
+                                                                  int* __restrict__ error_flag, float act_limit,
+                                                                  GemmGroup grp) {
   constexpr uint32_t A_BYTES = TG_BM * TG_BK * 2, B_BYTES = BN * TG_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
@@ -146,7 +159,9 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 gate with 128 up columns");
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;          // output columns per tile
-  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN_OUT - 1) / BN_OUT;
+  const bool grouped = grp.tile_expert != nullptr;
+  if (grouped) pdl_wait();            // the list of tiles is the work of the kernels before this one
+  const int tiles_m = grouped ? *grp.num_tiles : (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN_OUT - 1) / BN_OUT;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
@@ -167,7 +182,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
     if (lane == 0 && !wait_test_unarmed()) {
       // The weights do not depend on the kernel before this one: the B tiles of the first stages
       // are requested before the wait for it, the A tiles (its output) after.
-      auto load_b = [&](int s, int kb, int n0) {
+      auto load_b = [&](int s, int kb, int n0) {      // n0 counts from the first row of the (expert's) matrix in w
         unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
         if constexpr (SWIGLU) {
           // the map's box is 128 rows: gate rows n0.., then up rows N + n0.. of the merged matrix
@@ -178,7 +193,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
         }
       };
       int early = 0;
-      if ((int)blockIdx.x < num_tiles) {
+      if ((int)blockIdx.x < num_tiles && !grouped) {
         const int n0 = ((int)blockIdx.x / tiles_m) * BN_OUT;
         early = num_kb < STAGES ? num_kb : STAGES;
         for (int kb = 0; kb < early; ++kb) {          // fresh barriers: nothing to wait for
@@ -189,7 +204,9 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
       pdl_wait();
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
+        const int mt = tile % tiles_m;
+        const int m0 = grouped ? grp.tile_row0[mt] : mt * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
+        const int w0 = grouped ? grp.tile_expert[mt] * grp.w_rows : 0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
@@ -197,7 +214,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
           if (it >= early) {
             if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            load_b(s, kb, n0);
+            load_b(s, kb, w0 + n0);
           }
           tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
         }
@@ -237,14 +254,16 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int b = t & 1;
-      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
+      const int mt = tile % tiles_m;
+      const int m0 = grouped ? grp.tile_row0[mt] : mt * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
+      const int m_end = grouped ? grp.offsets[grp.tile_expert[mt] + 1] : M;       // rows from here on are not this tile's
       if (!mbar_wait(&acc_full[b], (t >> 1) & 1) || failed) {
         if (lane == 0) atomicExch(error_flag, WAIT_FAILED_GEMM_TCGEN05);
         break;
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
-      drain_tile<BN, TOut, SWIGLU>(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN), row, M, N, n0, out, act_limit);
+      drain_tile<BN, TOut, SWIGLU>(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN), row, m_end, N, n0, out, act_limit);
       // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -426,15 +445,16 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
 
 template <int BN, int STAGES, typename TOut, int SWIGLU = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
-                     cudaStream_t stream, float act_limit = 0.f) {
+                     cudaStream_t stream, float act_limit = 0.f, const GemmGroup& grp = GemmGroup(), int max_row_tiles = 0) {
   const size_t smem = (size_t)STAGES * (TG_BM + BN) * TG_BK * 2 + 1024;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
-  const int num_tiles = ((N + BN_OUT - 1) / BN_OUT) * ((M + TG_BM - 1) / TG_BM);
+  const int row_tiles = grp.tile_expert ? max_row_tiles : (M + TG_BM - 1) / TG_BM;
+  const int num_tiles = ((N + BN_OUT - 1) / BN_OUT) * row_tiles;
   const int ctas = num_tiles < 148 ? num_tiles : 148;     // one persistent CTA per SM
-  return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag, act_limit);
+  return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag, act_limit, grp);
 }
 
 template <int STAGES, typename TOut, int SWIGLU>
@@ -511,4 +531,27 @@ extern "C" int ts_gemm_tcgen05_gated(const void* x, const void* w, void* out, in
   }
   if (pair) return launch_tc_pair<6, bf16, GATED_GELU_TANH>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
   return launch_tc<256, 4, bf16, GATED_GELU_TANH>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+}
+
+// The experts' products of a routed feed-forward over rows sorted by expert (GemmGroup above): x is
+// [picks, K] in the sorted order, w [experts, N (gated: 2 N), K], out [picks, N] bf16; gated: out =
+// silu(gate) * up. The tile list must have been made for tiles of 128 rows. K % 8 == 0.
+extern "C" int ts_moe_gemm_tcgen05(const void* x, const void* w, void* out, int picks, int N, int K, int experts, int gated,
+                                   const int* offsets, const int* tile_expert, const int* tile_row0, const int* num_tiles,
+                                   int max_tiles, int* error_flag, cudaStream_t stream) {
+  if (picks <= 0 || N <= 0 || max_tiles <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr || experts <= 0) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TS_ERR_UNSUPPORTED;
+  GemmGroup grp;
+  grp.tile_expert = tile_expert; grp.tile_row0 = tile_row0; grp.offsets = offsets; grp.num_tiles = num_tiles;
+  grp.w_rows = gated ? 2 * N : N;
+  const long long w_total = (long long)experts * grp.w_rows;
+  if (w_total > 0x7fffffffLL) return TS_ERR_UNSUPPORTED;
+  CUtensorMap mx, mw;
+  if (gated) {
+    if (!make_map(&mx, x, picks, K, TG_BM) || !make_map(&mw, w, (int)w_total, K, 128)) return TS_ERR_UNSUPPORTED;
+    return launch_tc<256, 4, bf16, GATED_SILU>(mx, mw, (bf16*)out, picks, N, K, error_flag, stream, 0.f, grp, max_tiles);
+  }
+  if (!make_map(&mx, x, picks, K, TG_BM) || !make_map(&mw, w, (int)w_total, K, 256)) return TS_ERR_UNSUPPORTED;
+  return launch_tc<256, 4, bf16>(mx, mw, (bf16*)out, picks, N, K, error_flag, stream, 0.f, grp, max_tiles);
 }

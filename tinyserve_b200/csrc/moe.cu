@@ -226,11 +226,13 @@ __global__ void __launch_bounds__(SG_THREADS) moe_gemm_simt_kernel(
 }
 
 // ------------------------------------------------------- products, tensor cores
-// bf16, K % 32 == 0, N % 8 == 0. A CTA of four warps takes a tile of 64 rows x 64 output columns
+// bf16, K % 64 == 0, N % 8 == 0. A CTA of four warps takes a tile of 64 rows x 64 output columns
 // (gated: 64 gate and 64 up columns); a warp 16 rows of it. Operands come through shared memory in
-// steps of 32 along K, three steps in flight (cp.async, 16 bytes a request; rows of 80 bytes keep
-// the ldmatrix reads free of bank conflicts).
-constexpr int TG_M = 64, TG_N = 64, TG_K = 32, TG_STAGES = 3, TG_THREADS = 128, TG_LD = TG_K + 8;
+// steps of 64 along K, four steps in flight (cp.async, 16 bytes a request; rows of 144 bytes keep
+// the ldmatrix reads free of bank conflicts): two CTAs an SM keep some 150 KB of requests in flight,
+// which is what streaming the experts' matrices at the memory's rate takes when a step has few rows.
+constexpr int TG_M = 64, TG_N = 64, TG_K = 64, TG_STAGES = 4, TG_THREADS = 128, TG_LD = TG_K + 8;
+constexpr int TG_CH = TG_K / 8;      // 16-byte pieces of a row of a stage
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -276,16 +278,16 @@ __global__ void __launch_bounds__(TG_THREADS) moe_gemm_mma_kernel(
   __syncthreads();
 
   auto stage_load = [&](int stage, int k0) {
-    // A: 64 rows x 4 chunks of 8 elements; B: NB x 64 rows x 4 chunks
-    for (int c = tid; c < TG_M * 4; c += TG_THREADS) {
-      const int r = c >> 2, ch = c & 3;
+    // A: 64 rows x TG_CH pieces of 8 elements; B: NB x 64 rows x TG_CH pieces
+    for (int c = tid; c < TG_M * TG_CH; c += TG_THREADS) {
+      const int r = c / TG_CH, ch = c - r * TG_CH;
       const long long ar = a_rows[r];
       const bf16* src = x + (size_t)(ar < 0 ? 0 : ar) * K + k0 + ch * 8;
       cp_async16(As + ((size_t)stage * TG_M + r) * TG_LD + ch * 8, src, ar >= 0);
     }
-    for (int c = tid; c < NB * TG_N * 4; c += TG_THREADS) {
-      const int g = c / (TG_N * 4), rest = c - g * (TG_N * 4);
-      const int r = rest >> 2, ch = rest & 3;
+    for (int c = tid; c < NB * TG_N * TG_CH; c += TG_THREADS) {
+      const int g = c / (TG_N * TG_CH), rest = c - g * (TG_N * TG_CH);
+      const int r = rest / TG_CH, ch = rest - r * TG_CH;
       const int n = n0 + r;
       const bf16* src = we + ((size_t)g * N + (n < N ? n : 0)) * K + k0 + ch * 8;
       cp_async16(Bs + (((size_t)stage * NB + g) * TG_N + r) * TG_LD + ch * 8, src, n < N);
@@ -354,6 +356,18 @@ __global__ void __launch_bounds__(TG_THREADS) moe_gemm_mma_kernel(
   }
 }
 
+// ------------------------------------------------------------------------ gather
+// xs[row, :] = x[token_of[row], :] in pieces of 16 bytes (for the product that takes its rows in the sorted order).
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ token_of, uint4* __restrict__ xs,
+                                  int picks, int pieces) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)picks * pieces; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / pieces;
+    xs[idx] = x[(size_t)token_of[row] * pieces + (idx - row * pieces)];
+  }
+}
+
 // ----------------------------------------------------------------------- combine
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
@@ -378,20 +392,22 @@ extern "C" int ts_moe_tile_rows() { return SG_M; }      // both product forms us
 
 // logits [T, E] float -> ids / weights / place [T, top]; counts [E] (zero on entry, zero again after the plan);
 // offsets [E + 1]; tile_expert / tile_row0 [max_tiles]; num_tiles [1]; row_of [T * top]; token_of [T * top].
+// tile_rows: rows of a tile of the list (64 for the products of this file, 128 for the tcgen05 product).
 extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top, int* ids, float* weights, int* place,
                             int* counts, int* offsets, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
-                            int* row_of, int* token_of, cudaStream_t stream) {
+                            int* row_of, int* token_of, int tile_rows, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  if (tile_rows != 64 && tile_rows != 128) return TS_ERR_BAD_ARGUMENT;
   const int picks = num_tokens * top;
-  const int most = picks < picks / SG_M + E ? picks : picks / SG_M + E;   // every tile has a row; an expert one ragged tile
+  const int most = picks < picks / tile_rows + E ? picks : picks / tile_rows + E;   // every tile has a row; an expert one ragged tile
   if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most) return TS_ERR_BAD_ARGUMENT;
   if (num_tokens <= 64 && E <= ROUTE_SMALL_MAX_EXPERTS)
-    return launch(moe_route_small_kernel, 1, ROUTE_SMALL_THREADS, 0, stream, logits, num_tokens, E, top, SG_M, ids, weights, place,
+    return launch(moe_route_small_kernel, 1, ROUTE_SMALL_THREADS, 0, stream, logits, num_tokens, E, top, tile_rows, ids, weights, place,
                   offsets, tile_expert, tile_row0, num_tiles, max_tiles, row_of, token_of);
   int st = launch(moe_route_kernel, (num_tokens * 32 + 127) / 128, 128, 0, stream, logits, num_tokens, E, top, ids,
                   weights, place, counts);
   if (st != 0) return st;
-  st = launch(moe_plan_kernel, 1, 32, 0, stream, counts, E, SG_M, offsets, tile_expert, tile_row0, num_tiles, max_tiles);
+  st = launch(moe_plan_kernel, 1, 32, 0, stream, counts, E, tile_rows, offsets, tile_expert, tile_row0, num_tiles, max_tiles);
   if (st != 0) return st;
   const int total = num_tokens * top;
   return launch(moe_scatter_kernel, (total + 255) / 256, 256, 0, stream, (const int*)ids, (const int*)place,
@@ -431,6 +447,15 @@ extern "C" int ts_moe_gemm(const void* x, const int* token_of, const void* w, vo
   if (dtype == TS_DTYPE_BF16) { if (gated) TS_MOE_CASE(bf16, true); TS_MOE_CASE(bf16, false); }
 #undef TS_MOE_CASE
   return TS_ERR_BAD_ARGUMENT;
+}
+
+extern "C" int ts_moe_gather(const void* x, const int* token_of, void* xs, int picks, int row_bytes, cudaStream_t stream) {
+  if (picks <= 0) return 0;
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || (((uintptr_t)x | (uintptr_t)xs) & 15)) return TS_ERR_UNSUPPORTED;
+  const int pieces = row_bytes / 16;
+  size_t blocks = ((size_t)picks * pieces + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch(moe_gather_kernel, (int)blocks, 256, 0, stream, (const uint4*)x, token_of, (uint4*)xs, picks, pieces);
 }
 
 extern "C" int ts_moe_combine(const void* y, const int* row_of, const float* weights, const void* shared_out, void* out,

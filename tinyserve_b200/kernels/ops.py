@@ -75,7 +75,9 @@ _SIGNATURES: dict[str, list[Any]] = {
                           _i, _i, _i, _vp],
     "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _i, _vp],
     "ts_latent_attention_mma_takes": [_i, _i],
-    "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp],
+    "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
+    "ts_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
+    "ts_moe_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp],
     "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -1356,17 +1358,32 @@ def transpose01(x: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------------------------------- experts
 MOE_TILE_ROWS = 64
-MOE_TENSOR_CORES = True
+MOE_TENSOR_CORES = True          # bf16: False sends every product of the experts to the CUDA-core form
+# From this many sorted rows a step (and at least an average tile's worth of rows per expert), bf16 products
+# of experts whose matrices are wide enough run on the tcgen05 product over tiles of 128 rows; smaller steps
+# run mma.sync tiles of 64 rows (a few rows per expert waste less of a tile, and no gather is needed).
+MOE_TCGEN05 = True
+MOE_TCGEN05_MIN_ROWS = 1024
+MOE_TCGEN05_MIN_COLS = 256
 
 
-def moe_max_tiles(num_tokens: int, top: int, experts: int) -> int:
+def moe_max_tiles(num_tokens: int, top: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
     """The most row tiles a step's sorted order can have: every tile holds a row, and an expert at
     most one ragged tile beyond its full ones."""
     picks = num_tokens * top
-    return max(1, min(picks, picks // MOE_TILE_ROWS + experts))
+    return max(1, min(picks, picks // tile_rows + experts))
 
 
-def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any) -> dict[str, Any]:
+def moe_tile_rows(num_tokens: int, top: int, experts: int, dtype: torch.dtype, widths: Sequence[int]) -> int:
+    """128 when the experts' products of this step go to the tcgen05 product (``widths``: the inner sizes
+    K and output sizes N of the two products), else 64. Depends only on the step's shape."""
+    picks = num_tokens * top
+    big = (MOE_TCGEN05 and MOE_TENSOR_CORES and dtype == torch.bfloat16 and picks >= MOE_TCGEN05_MIN_ROWS
+           and picks >= 64 * experts and all(w % 8 == 0 and w >= MOE_TCGEN05_MIN_COLS for w in widths))
+    return 128 if big else MOE_TILE_ROWS
+
+
+def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
     """From router logits ``[T, E]`` float32: every token's ``top`` experts (largest logits, ties to
     the lower index), their weights (softmax over the picked logits only), and the sorted order in
     which the products run: rows grouped by expert, cut into tiles. ``counts`` is ``[E]`` int32,
@@ -1374,9 +1391,9 @@ def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any) 
     t, e = logits.shape
     if not 0 < top <= min(e, 32) or counts.shape != (e,):
         raise KernelError("moe_route: top must be between 1 and min(experts, 32); counts one per expert")
-    picks, tiles = t * top, moe_max_tiles(t, top, e)
+    picks, tiles = t * top, moe_max_tiles(t, top, e, tile_rows)
     ints = arena.take((4 * picks + e + 1 + 2 * tiles + 1,), torch.int32)
-    plan = {"top": top, "experts": e, "max_tiles": tiles, "picks": picks,
+    plan = {"top": top, "experts": e, "max_tiles": tiles, "picks": picks, "tile_rows": tile_rows,
             "ids": ints[:picks], "place": ints[picks: 2 * picks], "row_of": ints[2 * picks: 3 * picks],
             "token_of": ints[3 * picks: 4 * picks], "offsets": ints[4 * picks: 4 * picks + e + 1]}
     at = 4 * picks + e + 1
@@ -1386,11 +1403,13 @@ def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any) 
         _dev(logits, "logits", torch.float32), t, e, top, plan["ids"].data_ptr(), plan["weights"].data_ptr(),
         plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),
         plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), tiles,
-        plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), _stream()), "moe_route", kernels=1 if t <= 64 else 3)
+        plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), tile_rows, _stream()), "moe_route",
+        kernels=1 if t <= 64 else 3)
     return plan
 
 
-def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str, Any], gated: bool, gather: bool) -> None:
+def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str, Any], gated: bool, gather: bool,
+             arena: Any = None) -> None:
     """The experts' products over the sorted order of ``plan``: for every sorted row r of expert e,
     ``out[r] = x_r W_e^T`` (``gated``: ``silu(x_r Wgate_e^T) * (x_r Wup_e^T)`` with ``w [E, 2 N, K]``,
     gate rows first; else ``w [E, N, K]``). ``gather``: ``x`` is ``[T, K]`` and row r reads its
@@ -1401,6 +1420,20 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str
         raise KernelError("moe_gemm: shapes")
     if x.dtype != w.dtype or out.dtype != x.dtype or (not gather and x.shape[0] != picks):
         raise KernelError("moe_gemm: dtypes, or rows of x")
+    if plan["tile_rows"] == 128:
+        # tiles of 128 rows: the tcgen05 product over the sorted rows (gathered first where x is by token)
+        if x.dtype != torch.bfloat16 or (gather and arena is None):
+            raise KernelError("moe_gemm: tiles of 128 rows are for bfloat16, with scratch for the gathered rows")
+        if gather:
+            xs = arena.take((picks, k), x.dtype)
+            _check(_fn("ts_moe_gather")(_dev(x, "x"), plan["token_of"].data_ptr(), _dev(xs, "xs"), picks, k * x.element_size(),
+                                        _stream()), "moe_gather")
+            x = xs
+        _check(_fn("ts_moe_gemm_tcgen05")(
+            _dev(x, "x"), _dev(w, "w"), _dev(out, "out"), picks, n, k, e, int(bool(gated)), plan["offsets"].data_ptr(),
+            plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), plan["max_tiles"],
+            _error_word(x.device).data_ptr(), _stream()), "moe_gemm_tcgen05")
+        return
     _check(_fn("ts_moe_gemm")(
         _dev(x, "x"), plan["token_of"].data_ptr() if gather else None, _dev(w, "w"), _dev(out, "out"),
         plan["offsets"].data_ptr(), plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(),

@@ -160,11 +160,12 @@ class RoutedExperts(FeedForward):
         t, arena = x.shape[0], ctx.arena
         logits = arena.take((t, self.experts), torch.float32)
         ops.gemm(x, self.w_router, logits)
-        plan = ops.moe_route(logits, self.top, self.counts, arena)
+        tile_rows = ops.moe_tile_rows(t, self.top, self.experts, ctx.dtype, (self.h, self.ff))
+        plan = ops.moe_route(logits, self.top, self.counts, arena, tile_rows)
         act = arena.take((t * self.top, self.ff), ctx.dtype)
-        ops.moe_gemm(x, self.w_gate_up, act, plan, gated=True, gather=True)
+        ops.moe_gemm(x, self.w_gate_up, act, plan, gated=True, gather=True, arena=arena)
         y = arena.take((t * self.top, self.h), ctx.dtype)
-        ops.moe_gemm(act, self.w_down, y, plan, gated=False, gather=False)
+        ops.moe_gemm(act, self.w_down, y, plan, gated=False, gather=False, arena=arena)
         shared = None
         if self.shared_ff is not None:
             sact = arena.take((t, self.shared_ff), ctx.dtype)
