@@ -377,15 +377,30 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
     const bf16* qrow = Qs + (size_t)(rg * 16 + (lane & 15)) * ld + (lane >> 4) * 8;
     const bf16* krow = Kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8;
-    for (int kk = 0; kk < D; kk += 16) {
-      uint32_t af[4], b0[4], b1[4];
-      lm_ldmatrix(af, qrow + kk);
-      lm_ldmatrix(b0, krow + kk);
-      lm_ldmatrix(b1, krow + (size_t)16 * ld + kk);
-      lm_mma(s[0], af, b0[0], b0[1]);
-      lm_mma(s[1], af, b0[2], b0[3]);
-      lm_mma(s[2], af, b1[0], b1[1]);
-      lm_mma(s[3], af, b1[2], b1[3]);
+    {
+      // operands of step kk + 16 are asked for before the products of step kk are issued: with two warps
+      // per scheduler nothing else hides the shared-memory latency
+      uint32_t fa[3][4], fb[3][4];
+      auto fetch = [&](uint32_t (&f)[3][4], int kk) {
+        lm_ldmatrix(f[0], qrow + kk);
+        lm_ldmatrix(f[1], krow + kk);
+        lm_ldmatrix(f[2], krow + (size_t)16 * ld + kk);
+      };
+      auto multiply = [&](const uint32_t (&f)[3][4]) {
+        lm_mma(s[0], f[0], f[1][0], f[1][1]);
+        lm_mma(s[1], f[0], f[1][2], f[1][3]);
+        lm_mma(s[2], f[0], f[2][0], f[2][1]);
+        lm_mma(s[3], f[0], f[2][2], f[2][3]);
+      };
+      int kk = 0;
+      fetch(fa, 0);
+      for (; kk + 32 <= D; kk += 32) {
+        fetch(fb, kk + 16);
+        multiply(fa);
+        if (kk + 32 < D) fetch(fa, kk + 32);
+        multiply(fb);
+      }
+      if (kk < D) multiply(fa);
     }
     // ---- mask, online softmax (base 2)
     float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -436,21 +451,29 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
       pf[ks][3] = lm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
     }
     const bf16* vrow = Kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
+    {
+      // step st = 2 jp + ks: 16 keys x 16 columns; the values of step st + 1 are asked for before the
+      // products of step st (columns from R on belong to nobody: neither fetched nor multiplied)
+      uint32_t vf[2][4];
+      if (col_base < R) lm_ldmatrix_t(vf[0], vrow + col_base);
 #pragma unroll
-    for (int jp = 0; jp < NB / 2; ++jp) {
-      const int col = col_base + jp * 16;
+      for (int st = 0; st < NB; ++st) {
+        const int jp = st >> 1, ks = st & 1;
+        const int col = col_base + jp * 16;
+        if (st + 1 < NB) {
+          const int ncol = col_base + ((st + 1) >> 1) * 16;
+          if (ncol < R) lm_ldmatrix_t(vf[(st + 1) & 1], vrow + (size_t)((st + 1) & 1) * 16 * ld + ncol);
+        }
+        if (ks == 0) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        o[2 * jp][e] *= (e & 2) ? corr_b : corr_a;
-        o[2 * jp + 1][e] *= (e & 2) ? corr_b : corr_a;
-      }
-      if (col < R) {                                 // warp-uniform; R % 16 == 0
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-          uint32_t vf[4];
-          lm_ldmatrix_t(vf, vrow + (size_t)ks * 16 * ld + col);
-          lm_mma(o[2 * jp], pf[ks], vf[0], vf[1]);
-          lm_mma(o[2 * jp + 1], pf[ks], vf[2], vf[3]);
+          for (int e = 0; e < 4; ++e) {
+            o[2 * jp][e] *= (e & 2) ? corr_b : corr_a;
+            o[2 * jp + 1][e] *= (e & 2) ? corr_b : corr_a;
+          }
+        }
+        if (col < R) {                                 // warp-uniform; R % 16 == 0
+          lm_mma(o[2 * jp], pf[ks], vf[st & 1][0], vf[st & 1][1]);
+          lm_mma(o[2 * jp + 1], pf[ks], vf[st & 1][2], vf[st & 1][3]);
         }
       }
     }
