@@ -20,7 +20,7 @@ import kernel_refs as refs
 import plain_guzovik as plain
 import replay_cases as cases
 from fegilix_cases import relative_error, run_steps
-from guzovik_cases import CONFIGS, FakeCtx, assert_rows_close, write_model
+from guzovik_cases import CONFIGS, FakeCtx, assert_rows_close, random_config, write_model
 from tiny_configs import random_prompt
 
 pytestmark = pytest.mark.gpu
@@ -455,6 +455,46 @@ def test_model_under_every_cut(folders, oracle, dtype, which, page) -> None:
         assert_rows_close(rows, torch.cat([want[rid] for rid in got]), dtype, f"{which}, schedule {n}")
 
 
+@pytest.mark.parametrize("seed", list(range(1, 13)))
+def test_configurations_drawn_at_random(seed, tmp_path) -> None:
+    """Sizes, head counts, windows, layer order, shared tensors, feed-forward kinds and constants drawn at
+    random; a prompt alone, decoded token by token, and mixed with others. float32 must equal the oracle.
+    bfloat16 is a sanity check here: with wide random weights some of these models amplify rounding (several
+    routed layers in a row, one expert of seven), the CUDA-core kernels on the same bfloat16 values land at the
+    same distance from the oracle, so the rows must only stay in the oracle's neighbourhood, and the same
+    prompt fed whole and decoded token by token must land at the same distance."""
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.model import DecoderModel
+    from tinyserve_b200.weights import write_random_model
+
+    cfg = random_config(seed)
+    folder = write_random_model(tmp_path, config_from_dict(cfg), seed, torch.bfloat16, std_scale=6.0)
+    w = plain.read_weights(folder, torch.float64)
+    reqs = {f"r{i}": random_prompt(n, cfg["vocab"], 300 + seed + 7 * i) for i, n in enumerate([2, 35, 260, 121])}
+    want = {rid: plain.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    page = [4, 8, 16, 32][seed % 4]
+    plans = [cases.mixed(reqs, seed), cases.whole("r2", reqs["r2"]), cases.tail_decoded("r2", reqs["r2"], 40), cases.portions("r3", reqs["r3"], seed)]
+    from guzovik_cases import row_errors
+
+    for dtype in DTYPES:
+        model = DecoderModel.from_folder(folder, dtype, "cuda")
+        medians = []
+        for n, steps in enumerate(plans):
+            got, _ = run_steps(model, page, steps, cases.max_live_tokens(steps))
+            rows = torch.cat([torch.stack([got[rid][p] for p in range(len(reqs[rid]))]) for rid in got])
+            oracle_rows = torch.cat([want[rid] for rid in got])
+            what = f"seed {seed}, schedule {n}: {json.dumps(cfg)[:300]}"
+            if dtype == torch.float32:
+                # a model that amplifies bfloat16 rounding to a tenth of the logits' spread amplifies 32-bit rounding too
+                assert_rows_close(rows, oracle_rows, dtype, what, limit32=1e-4)
+                continue
+            assert not rows.isnan().any(), what
+            medians.append(float(row_errors(rows, oracle_rows).median()))
+            assert medians[-1] < 0.25, f"{what}: median relative error {medians[-1]:.3g}"
+        if medians:
+            assert abs(medians[1] - medians[2]) <= 0.25 * max(medians[1], 1e-3), f"seed {seed}: whole {medians[1]:.3g}, decoded {medians[2]:.3g}"
+
+
 def test_model_with_its_experts_on_the_tcgen05_product(folders, oracle) -> None:
     """The thresholds lowered so that the small model's prompt portions take the tiles of 128 rows."""
     from tinyserve_b200.kernels import ops
@@ -521,6 +561,20 @@ def test_greedy_generation_through_llm(folders, graphs, which) -> None:
     assert llm.generate(prompts, max_new_tokens=8) == want
     assert (llm.engine.runner.num_graph_steps > 0) == graphs
     assert all(g.allocator.num_used == 0 for g in llm.cache.groups)
+
+
+def test_command_line(folders) -> None:
+    cfg, w = plain.read_config(folders["A"]), plain.read_weights(folders["A"], torch.float64)
+    prompt = random_prompt(19, cfg["vocab"], 77)
+    want = plain.greedy(cfg, w, prompt, 8)
+    cmd = [sys.executable, str(ROOT / "bin" / "generate"), "--model-dir", str(folders["A"]), "--prompt-ids", ",".join(map(str, prompt)),
+           "--max-new-tokens", "8", "--dtype", "float32", "--block-size", "8"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert f"new ids:    {want}" in out.stdout
+    out = subprocess.run(cmd + ["--temperature", "0.8", "--top-p", "0.9", "--seed", "3", "--num-samples", "2"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "2 samples, 16 tokens" in out.stdout, out.stdout + out.stderr[-1000:]
 
 
 def test_trace_run_subprocess(folders, oracle, tmp_path) -> None:
