@@ -262,13 +262,12 @@ __device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem, bool
 }
 __device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void lm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void lm_ldmatrix(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+// `s`: an address in the shared window (32 bits), so that the loops add plain offsets
+__device__ __forceinline__ void lm_ldmatrix(uint32_t (&r)[4], uint32_t s) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
-__device__ __forceinline__ void lm_ldmatrix_t(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void lm_ldmatrix_t(uint32_t (&r)[4], uint32_t s) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
@@ -327,10 +326,12 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
   const int k_begin = (k_lo / LM_TK) * LM_TK;
   const int tiles = k_hi > k_begin ? (k_hi - k_begin + LM_TK - 1) / LM_TK : 0;
 
+  // a warp fetches rows warp, warp + 8, ... of a tile, a lane every 32nd piece of a row: one look-up in the
+  // block table per row and no division per piece
   auto load_tile = [&](int buf, int k0) {
     bf16* dst = Ks + (size_t)buf * LM_TK * ld;
-    for (int c = tid; c < LM_TK * chunks; c += LM_THREADS) {
-      const int kk = c / chunks, piece = c - kk * chunks;
+#pragma unroll
+    for (int kk = warp; kk < LM_TK; kk += LM_THREADS / 32) {
       const int kpos = k0 + kk;
       const bool ok = kpos >= k_lo && kpos < k_hi;
       size_t crow = 0;
@@ -338,19 +339,22 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
         const int pg = kpos / a.page_size;
         crow = (size_t)table[pg] * a.page_size + (kpos - pg * a.page_size);
       }
-      lm_cp_async16(dst + (size_t)kk * ld + piece * 8, cache + crow * D + piece * 8, ok);
+      const bf16* src = cache + crow * D;
+      bf16* drow = dst + (size_t)kk * ld;
+      for (int piece = lane; piece < chunks; piece += 32) lm_cp_async16(drow + piece * 8, src + piece * 8, ok);
     }
   };
   // the queries (rows beyond the CTA's own are zero) and the first tile
-  for (int c = tid; c < LM_ROWS * chunks; c += LM_THREADS) {
-    const int r = c / chunks, piece = c - r * chunks;
+  for (int r = warp; r < LM_ROWS; r += LM_THREADS / 32) {
     const bool ok = r < nrows;
     const int tt = ok ? r / nh : 0, hh = ok ? r - tt * nh : 0;
-    lm_cp_async16(Qs + (size_t)r * ld + piece * 8, q + ((size_t)(row0 + t0 + tt) * a.heads + h0 + hh) * D + piece * 8, ok);
+    const bf16* src = q + ((size_t)(row0 + t0 + tt) * a.heads + h0 + hh) * D;
+    for (int piece = lane; piece < chunks; piece += 32) lm_cp_async16(Qs + (size_t)r * ld + piece * 8, src + piece * 8, ok);
   }
   if (tiles > 0) load_tile(0, k_begin);
   lm_commit();
 
+  const uint32_t q_base = (uint32_t)__cvta_generic_to_shared(Qs);
   const int r_lo = rg * 16 + (lane >> 2), r_hi = r_lo + 8;          // this thread's two rows of the CTA
   const int qpos_a = r_lo < nrows ? first_pos + t0 + r_lo / nh : -1;
   const int qpos_b = r_hi < nrows ? first_pos + t0 + r_hi / nh : -1;
@@ -368,23 +372,23 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     lm_commit();
     lm_wait<1>();
     __syncthreads();
-    const bf16* Kt = Ks + (size_t)(it & 1) * LM_TK * ld;
+    const uint32_t Kt = (uint32_t)__cvta_generic_to_shared(Ks + (size_t)(it & 1) * LM_TK * ld);   // bytes from here on
     // ---- S = Q K^T for 16 rows x 32 keys
     float s[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-    const bf16* qrow = Qs + (size_t)(rg * 16 + (lane & 15)) * ld + (lane >> 4) * 8;
-    const bf16* krow = Kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8;
+    const uint32_t qrow = q_base + 2u * (uint32_t)((rg * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
+    const uint32_t krow = Kt + 2u * (uint32_t)(((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8);
     {
       // operands of step kk + 16 are asked for before the products of step kk are issued: with two warps
       // per scheduler nothing else hides the shared-memory latency
       uint32_t fa[3][4], fb[3][4];
       auto fetch = [&](uint32_t (&f)[3][4], int kk) {
-        lm_ldmatrix(f[0], qrow + kk);
-        lm_ldmatrix(f[1], krow + kk);
-        lm_ldmatrix(f[2], krow + (size_t)16 * ld + kk);
+        lm_ldmatrix(f[0], qrow + 2u * kk);
+        lm_ldmatrix(f[1], krow + 2u * kk);
+        lm_ldmatrix(f[2], krow + 2u * (uint32_t)(16 * ld + kk));
       };
       auto multiply = [&](const uint32_t (&f)[3][4]) {
         lm_mma(s[0], f[0], f[1][0], f[1][1]);
@@ -450,19 +454,19 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
       pf[ks][2] = lm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]);
       pf[ks][3] = lm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
     }
-    const bf16* vrow = Kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
+    const uint32_t vrow = Kt + 2u * (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8);
     {
       // step st = 2 jp + ks: 16 keys x 16 columns; the values of step st + 1 are asked for before the
       // products of step st (columns from R on belong to nobody: neither fetched nor multiplied)
       uint32_t vf[2][4];
-      if (col_base < R) lm_ldmatrix_t(vf[0], vrow + col_base);
+      if (col_base < R) lm_ldmatrix_t(vf[0], vrow + 2u * col_base);
 #pragma unroll
       for (int st = 0; st < NB; ++st) {
         const int jp = st >> 1, ks = st & 1;
         const int col = col_base + jp * 16;
         if (st + 1 < NB) {
           const int ncol = col_base + ((st + 1) >> 1) * 16;
-          if (ncol < R) lm_ldmatrix_t(vf[(st + 1) & 1], vrow + (size_t)((st + 1) & 1) * 16 * ld + ncol);
+          if (ncol < R) lm_ldmatrix_t(vf[(st + 1) & 1], vrow + 2u * (uint32_t)(((st + 1) & 1) * 16 * ld + ncol));
         }
         if (ks == 0) {
 #pragma unroll
