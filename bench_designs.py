@@ -68,7 +68,7 @@ def guzovik_config(s: dict) -> dict:
 
 
 DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config}
-NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route", "moe_gemm",
+NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route_from", "moe_route", "moe_gemm",
            "moe_combine", "gemm_gated", "hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
            "causal_conv_silu", "qkv_prepare"]
 OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
@@ -160,6 +160,8 @@ class DesignBench(Bench):
                 return nbytes(a[0], a[2], a[3]), 0.0
             if name == "moe_route":
                 return nbytes(a[0]) * 3.0, 0.0
+            if name == "moe_route_from":
+                return nbytes(a[0], a[1]), 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
             if name == "post_norm_add_rms_norm":      # the stream read and written, the pending output, the result
                 return 2.0 * nbytes(a[0]) + nbytes(a[1], a[9]), 0.0
             if name == "latent_prepare":

@@ -267,6 +267,10 @@ def moe_tile_rows(num_tokens, top, experts, dtype, widths) -> int:
     return 64
 
 
+def moe_route_from(x, w_router, top, counts, arena=None, tile_rows=64) -> dict:
+    return moe_route(x.float() @ w_router.float().t(), top, counts, arena, tile_rows)
+
+
 def moe_route(logits, top, counts, arena=None, tile_rows=64) -> dict:
     """The same plan as the kernels make, with the rows of an expert in token order."""
     t, e = logits.shape
@@ -462,7 +466,7 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, st
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
           "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
           "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
-          "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows",
+          "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows", "moe_route_from",
           "moe_route", "moe_gemm", "moe_combine"]
 
 

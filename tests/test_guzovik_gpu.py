@@ -395,6 +395,34 @@ def test_routed_experts_on_the_tcgen05_product(tokens, experts, top, hidden, ff,
         torch.testing.assert_close(out, out_r.float(), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, experts, top, hidden", [(1, 8, 3, 256), (8, 16, 3, 1024), (64, 5, 2, 36), (9, 33, 4, 40), (300, 8, 2, 128), (4, 700, 8, 64)])
+def test_router_inside_the_routing_kernel(dtype, tokens, experts, top, hidden) -> None:
+    """Small steps can form the router's logits in the CTA that routes; larger ones go through the product.
+    Both pick what the reference picks (the inputs are made so that no two logits of a token lie close)."""
+    from tinyserve_b200.kernels import ops
+
+    for work in (1 << 22, 0):
+        ops.MOE_ROUTE_FUSED_MAX_WORK = work
+        try:
+            _router_case(ops, dtype, tokens, experts, top, hidden)
+        finally:
+            ops.MOE_ROUTE_FUSED_MAX_WORK = 0
+
+
+def _router_case(ops, dtype, tokens, experts, top, hidden) -> None:
+    x = _rand(tokens, hidden, seed=1, dtype=dtype)
+    w = _rand(experts, hidden, seed=2, dtype=dtype)
+    w[:, 0] += (torch.arange(experts, device="cuda") * 0.7).to(dtype)        # spread the logits apart
+    x[:, 0] = 3.0
+    counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    plan = ops.moe_route_from(x, w, top, counts, Arena())
+    want = refs.moe_route_from(x, w, top, None)
+    assert torch.equal(plan["ids"], want["ids"]) and torch.equal(plan["offsets"], want["offsets"])
+    torch.testing.assert_close(plan["weights"], want["weights"], atol=2e-3, rtol=2e-3)
+    assert sorted(plan["row_of"].tolist()) == list(range(tokens * top)) and counts.abs().max() == 0
+
+
 def test_a_token_alone_and_in_a_crowd_takes_the_same_experts_path() -> None:
     """float32: a row's sums do not depend on what shares its tile."""
     from tinyserve_b200.kernels import ops

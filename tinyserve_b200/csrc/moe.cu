@@ -70,8 +70,12 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int num_token
 // A step of few tokens (decoding): route, plan and scatter by ONE CTA, the queue counters in shared
 // memory, so that the three launches become one.
 constexpr int ROUTE_SMALL_THREADS = 512, ROUTE_SMALL_MAX_EXPERTS = 1024;
+// With `x` (and the router's matrix `w`, both of type T) the CTA first forms the router logits itself,
+// logits[t, e] = x[t] . w[e] with 32-bit sums, so that the router's product is no launch of its own either.
+template <typename T>
 __global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
-    const float* __restrict__ logits, int num_tokens, int E, int top, int tile_rows, int* __restrict__ ids,
+    const T* __restrict__ x, const T* __restrict__ w, int hidden,
+    float* logits, int num_tokens, int E, int top, int tile_rows, int* __restrict__ ids,
     float* __restrict__ weights, int* __restrict__ place, int* __restrict__ offsets, int* __restrict__ tile_expert,
     int* __restrict__ tile_row0, int* __restrict__ num_tiles, int max_tiles, int* __restrict__ row_of,
     int* __restrict__ token_of) {
@@ -80,8 +84,34 @@ __global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
   pdl_trigger();
   for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
   pdl_wait();
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (x != nullptr) {
+    constexpr int VEC = Vec<T>::N;
+    const bool wide = hidden % VEC == 0 && ((((uintptr_t)x) | ((uintptr_t)w)) & 15) == 0;
+    for (int pair = warp; pair < num_tokens * E; pair += warps) {
+      const int t = pair / E, e = pair - t * E;
+      const T* xr = x + (size_t)t * hidden;
+      const T* wr = w + (size_t)e * hidden;
+      float sum = 0.f;
+      if (wide) {
+        for (int i = lane * VEC; i < hidden; i += 32 * VEC) {
+          Vec<T> a, b;
+          a.load(xr + i);
+          b.load(wr + i);
+          float fa[VEC], fb[VEC];
+          a.unpack(fa);
+          b.unpack(fb);
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) sum = fmaf(fa[q], fb[q], sum);
+        }
+      } else {
+        for (int i = lane; i < hidden; i += 32) sum = fmaf(to_float(xr[i]), to_float(wr[i]), sum);
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) logits[pair] = sum;
+    }
+  }
+  __syncthreads();
   for (int t = warp; t < num_tokens; t += warps) route_token(logits + (size_t)t * E, t, lane, E, top, ids, weights, place, counts);
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -402,8 +432,9 @@ extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top,
   const int most = picks < picks / tile_rows + E ? picks : picks / tile_rows + E;   // every tile has a row; an expert one ragged tile
   if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most) return TS_ERR_BAD_ARGUMENT;
   if (num_tokens <= 64 && E <= ROUTE_SMALL_MAX_EXPERTS)
-    return launch(moe_route_small_kernel, 1, ROUTE_SMALL_THREADS, 0, stream, logits, num_tokens, E, top, tile_rows, ids, weights, place,
-                  offsets, tile_expert, tile_row0, num_tiles, max_tiles, row_of, token_of);
+    return launch(moe_route_small_kernel<float>, 1, ROUTE_SMALL_THREADS, 0, stream, (const float*)nullptr, (const float*)nullptr, 0,
+                  const_cast<float*>(logits), num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0,
+                  num_tiles, max_tiles, row_of, token_of);
   int st = launch(moe_route_kernel, (num_tokens * 32 + 127) / 128, 128, 0, stream, logits, num_tokens, E, top, ids,
                   weights, place, counts);
   if (st != 0) return st;
@@ -412,6 +443,29 @@ extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top,
   const int total = num_tokens * top;
   return launch(moe_scatter_kernel, (total + 255) / 256, 256, 0, stream, (const int*)ids, (const int*)place,
                 (const int*)offsets, total, top, row_of, token_of);
+}
+
+// The same for a step of up to 64 tokens with the router's product inside: logits (scratch, [T, E] float) are
+// formed from x [T, hidden] and w_router [E, hidden] of `dtype` by the one CTA that routes.
+extern "C" int ts_moe_route_fused(const void* x, const void* w_router, int hidden, int dtype, float* logits, int num_tokens,
+                                  int E, int top, int* ids, float* weights, int* place, int* offsets, int* tile_expert,
+                                  int* tile_row0, int* num_tiles, int max_tiles, int* row_of, int* token_of, int tile_rows,
+                                  cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (tile_rows != 64 && tile_rows != 128) return TS_ERR_BAD_ARGUMENT;
+  const int picks = num_tokens * top;
+  const int most = picks < picks / tile_rows + E ? picks : picks / tile_rows + E;
+  if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most || hidden <= 0 || !x || !w_router) return TS_ERR_BAD_ARGUMENT;
+  if (num_tokens > 64 || E > ROUTE_SMALL_MAX_EXPERTS) return TS_ERR_UNSUPPORTED;
+  if (dtype == TS_DTYPE_F32)
+    return launch(moe_route_small_kernel<float>, 1, ROUTE_SMALL_THREADS, 0, stream, (const float*)x, (const float*)w_router, hidden,
+                  logits, num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0, num_tiles, max_tiles,
+                  row_of, token_of);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(moe_route_small_kernel<bf16>, 1, ROUTE_SMALL_THREADS, 0, stream, (const bf16*)x, (const bf16*)w_router, hidden,
+                  logits, num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0, num_tiles, max_tiles,
+                  row_of, token_of);
+  return TS_ERR_BAD_ARGUMENT;
 }
 
 // out[row, :] for every row of the sorted order: x rows are taken through `token_of` when it is

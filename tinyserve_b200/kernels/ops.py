@@ -76,6 +76,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _i, _vp],
     "ts_latent_attention_mma_takes": [_i, _i],
     "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
+    "ts_moe_route_fused": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
     "ts_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
     "ts_moe_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp],
     "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -1383,14 +1384,14 @@ def moe_tile_rows(num_tokens: int, top: int, experts: int, dtype: torch.dtype, w
     return 128 if big else MOE_TILE_ROWS
 
 
-def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
-    """From router logits ``[T, E]`` float32: every token's ``top`` experts (largest logits, ties to
-    the lower index), their weights (softmax over the picked logits only), and the sorted order in
-    which the products run: rows grouped by expert, cut into tiles. ``counts`` is ``[E]`` int32,
-    zero before the call and zero again after it. Returns the plan's device arrays."""
-    t, e = logits.shape
-    if not 0 < top <= min(e, 32) or counts.shape != (e,):
-        raise KernelError("moe_route: top must be between 1 and min(experts, 32); counts one per expert")
+# Multiply-adds up to which the one routing CTA of a small step forms the router's logits itself instead of a
+# product launched before it. Off (0): measured on B200 at 8 tokens, 16 experts, width 1,024 the recorded decode
+# step of six layers went from 0.606 to 0.640 ms with it (84 to 79 kernels): one SM's 16 warps take about 8 us
+# over the 128 dot products that the few-row product spreads over the machine in 3.
+MOE_ROUTE_FUSED_MAX_WORK = 0
+
+
+def _moe_plan(t: int, e: int, top: int, arena: Any, tile_rows: int) -> dict[str, Any]:
     picks, tiles = t * top, moe_max_tiles(t, top, e, tile_rows)
     ints = arena.take((4 * picks + e + 1 + 2 * tiles + 1,), torch.int32)
     plan = {"top": top, "experts": e, "max_tiles": tiles, "picks": picks, "tile_rows": tile_rows,
@@ -1399,6 +1400,42 @@ def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, 
     at = 4 * picks + e + 1
     plan["tile_expert"], plan["tile_row0"], plan["num_tiles"] = ints[at: at + tiles], ints[at + tiles: at + 2 * tiles], ints[at + 2 * tiles:]
     plan["weights"] = arena.take((picks,), torch.float32)
+    return plan
+
+
+def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, counts: torch.Tensor, arena: Any,
+                   tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
+    """Router logits ``x W_router^T`` (32-bit sums and output) and :func:`moe_route` on them. A step of few
+    tokens can do both in the one CTA that routes (no launch for the router's product); its sums run in
+    another order than the product's, so a token's logits differ in the last bits between the two;
+    switched by ``MOE_ROUTE_FUSED_MAX_WORK``, off by default)."""
+    t, k = x.shape
+    e = w_router.shape[0]
+    if w_router.shape[1] != k or x.dtype != w_router.dtype:
+        raise KernelError("moe_route_from: shapes or dtypes")
+    logits = arena.take((t, e), torch.float32)
+    if t <= 64 and e <= 1024 and t * e * k <= MOE_ROUTE_FUSED_MAX_WORK and 0 < top <= min(e, 32):
+        plan = _moe_plan(t, e, top, arena, tile_rows)
+        _check(_fn("ts_moe_route_fused")(
+            _dev(x, "x"), _dev(w_router, "w_router"), k, _code(x.dtype), _dev(logits, "logits", torch.float32), t, e, top,
+            plan["ids"].data_ptr(), plan["weights"].data_ptr(), plan["place"].data_ptr(), plan["offsets"].data_ptr(),
+            plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), plan["max_tiles"],
+            plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), tile_rows, _stream()), "moe_route_fused")
+        return plan
+    gemm(x, w_router, logits)
+    return moe_route(logits, top, counts, arena, tile_rows)
+
+
+def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
+    """From router logits ``[T, E]`` float32: every token's ``top`` experts (largest logits, ties to
+    the lower index), their weights (softmax over the picked logits only), and the sorted order in
+    which the products run: rows grouped by expert, cut into tiles. ``counts`` is ``[E]`` int32,
+    zero before the call and zero again after it. Returns the plan's device arrays."""
+    t, e = logits.shape
+    if not 0 < top <= min(e, 32) or counts.shape != (e,):
+        raise KernelError("moe_route: top must be between 1 and min(experts, 32); counts one per expert")
+    tiles = moe_max_tiles(t, top, e, tile_rows)
+    plan = _moe_plan(t, e, top, arena, tile_rows)
     _check(_fn("ts_moe_route")(
         _dev(logits, "logits", torch.float32), t, e, top, plan["ids"].data_ptr(), plan["weights"].data_ptr(),
         plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),

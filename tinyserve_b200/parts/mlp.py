@@ -158,10 +158,8 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         t, arena = x.shape[0], ctx.arena
-        logits = arena.take((t, self.experts), torch.float32)
-        ops.gemm(x, self.w_router, logits)
         tile_rows = ops.moe_tile_rows(t, self.top, self.experts, ctx.dtype, (self.h, self.ff))
-        plan = ops.moe_route(logits, self.top, self.counts, arena, tile_rows)
+        plan = ops.moe_route_from(x, self.w_router, self.top, self.counts, arena, tile_rows)
         act = arena.take((t * self.top, self.ff), ctx.dtype)
         ops.moe_gemm(x, self.w_gate_up, act, plan, gated=True, gather=True, arena=arena)
         y = arena.take((t * self.top, self.h), ctx.dtype)
