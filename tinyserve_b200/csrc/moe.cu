@@ -414,6 +414,50 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
   }
 }
 
+// The same with 16-byte accesses (hidden a multiple of the vector length, aligned rows): the picks' rows
+// are asked for together, up to eight at a time.
+template <typename T>
+__global__ void moe_combine_vec_kernel(const T* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
+                                       const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden) {
+  constexpr int VEC = Vec<T>::N;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int* rows = row_of + (size_t)t * top;
+  const float* wt = weights + (size_t)t * top;
+  for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int j0 = 0; j0 < top; j0 += 8) {
+      Vec<T> part[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < top) part[u].load(y + (size_t)rows[j0 + u] * hidden + c);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < top) {
+          float f[VEC];
+          part[u].unpack(f);
+          const float a = wt[j0 + u];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[e] = fmaf(a, f[e], acc[e]);
+        }
+    }
+    if (shared_out) {
+      Vec<T> sv;
+      sv.load(shared_out + (size_t)t * hidden + c);
+      float f[VEC];
+      sv.unpack(f);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += f[e];
+    }
+    Vec<T> ov;
+    ov.pack(acc);
+    ov.store(out + (size_t)t * hidden + c);
+  }
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -516,6 +560,18 @@ extern "C" int ts_moe_combine(const void* y, const int* row_of, const float* wei
                               int num_tokens, int top, int hidden, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
+  const int vec = dtype == TS_DTYPE_F32 ? 4 : 8;
+  if (hidden % vec == 0 && (((uintptr_t)y | (uintptr_t)shared_out | (uintptr_t)out) & 15) == 0) {
+    int vthreads = 32;
+    while (vthreads < 256 && vthreads * vec < hidden) vthreads <<= 1;
+    if (dtype == TS_DTYPE_F32)
+      return launch(moe_combine_vec_kernel<float>, num_tokens, vthreads, 0, stream, (const float*)y, row_of, weights,
+                    (const float*)shared_out, (float*)out, top, hidden);
+    if (dtype == TS_DTYPE_BF16)
+      return launch(moe_combine_vec_kernel<bf16>, num_tokens, vthreads, 0, stream, (const bf16*)y, row_of, weights,
+                    (const bf16*)shared_out, (bf16*)out, top, hidden);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   if (dtype == TS_DTYPE_F32)
     return launch(moe_combine_kernel<float>, num_tokens, threads, 0, stream, (const float*)y, row_of, weights,
                   (const float*)shared_out, (float*)out, top, hidden);
