@@ -232,7 +232,8 @@ def _window_case(dtype, heads, groups, d, dv, page, lens, news, window, edge=Non
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, groups, d, dv, page, window", [
     (4, 2, 32, 16, 4, 7), (8, 1, 48, 48, 16, 96), (4, 2, 64, 64, 16, 40), (4, 4, 64, 64, 16, 33), (4, 1, 128, 128, 16, 100),
-    (8, 2, 128, 128, 32, 1), (6, 3, 64, 64, 8, 200), (2, 2, 24, 40, 8, 19)])
+    (8, 2, 128, 128, 32, 1), (6, 3, 64, 64, 8, 200), (2, 2, 24, 40, 8, 19), (32, 1, 64, 64, 16, 100), (24, 1, 128, 128, 16, 60),
+    (40, 2, 64, 64, 16, 0), (20, 1, 48, 48, 16, 96)])
 def test_window_attention_with_an_added_one_kernels(dtype, heads, groups, d, dv, page, window) -> None:
     """CUDA-core kernels and, in bfloat16 at head sizes 64 / 128, the tensor-core prompt and decode kernels,
     with the fixed sink and a window together; prompt portions beside single tokens."""
